@@ -58,6 +58,9 @@ class CacheNeeds:
 
     kv: PagedKVSpec | None = None
     state: StateSpec | None = None
+    # a state that stays the run's own where it reads another run's cache (what a block
+    # keeps beside its mixer: the last inputs of a short convolution, say)
+    own_state: StateSpec | None = None
 
 
 @dataclass
@@ -127,7 +130,11 @@ class CacheManager:
         self._requests: dict[object, RequestCache] = {}
         self.guarded: list = []          # GuardedBuffers behind the groups' storage (CUDA only)
         by_spec: dict[PagedKVSpec, LayerGroup] = {}
+        self._own_state: dict[int, object] = {}  # run -> its own state tensor, never shared
+        self._own_state_specs: dict[int, StateSpec] = {}
         for run, need in enumerate(needs):
+            if need is not None and getattr(need, "own_state", None) is not None:
+                self._own_state_specs[run] = need.own_state
             if run in self.shares:
                 continue
             if need is None:
@@ -180,6 +187,10 @@ class CacheManager:
             self._run_state[run] = torch.zeros(
                 (self.max_requests + 1, *spec.shape), dtype=getattr(torch, spec.dtype), device=self.device
             )
+        for run, spec in self._own_state_specs.items():
+            self._own_state[run] = torch.zeros(
+                (self.max_requests + 1, *spec.shape), dtype=getattr(torch, spec.dtype), device=self.device
+            )
 
     def bytes_per_token(self) -> int:
         """Bytes of keys and values one token occupies over all groups (unwindowed view)."""
@@ -221,6 +232,7 @@ class CacheManager:
             group=self.group_of_run(run),
             owns=run not in self.shares,
             state=self.state_of_run(run),
+            own_state=self._own_state.get(run),
         )
 
     def state_of_run(self, run: int):
@@ -247,7 +259,7 @@ class CacheManager:
         if key in self._requests:
             raise ValueError(f"request {key!r} is already live")
         slot = self.slots.lease()
-        for state in self._run_state.values():
+        for state in (*self._run_state.values(), *self._own_state.values()):
             state[slot].zero_()
         entry = RequestCache(key, slot, 0, [BlockTable() for _ in self.groups])
         self._requests[key] = entry

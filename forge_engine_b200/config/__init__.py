@@ -11,8 +11,10 @@ from .registry import (
 )
 from .specs import (
     AttentionSpec,
+    DenseMLPSpec,
     DifferentialSpec,
     GatedMLPSpec,
+    GatedRecurrenceSpec,
     LatentAttentionSpec,
     LayerNormSpec,
     LayerSpec,
@@ -23,9 +25,11 @@ from .specs import (
     RotarySpec,
     RoutedMLPSpec,
     RunSpec,
+    SandwichConvSpec,
     StreamMixSpec,
 )
 from .tekilorn import TekilornConfig
+from .zabutar import ZabutarConfig
 from .zofadra import ZofadraConfig
 
 register_architecture(
@@ -41,12 +45,19 @@ register_architecture(
     replace=True,
 )
 
+register_architecture(
+    Architecture("Zabutar", ZabutarConfig.from_dict, ZabutarConfig.to_model_spec),
+    replace=True,
+)
+
 __all__ = [
     "Architecture",
     "AttentionSpec",
+    "DenseMLPSpec",
     "DifferentialSpec",
     "EngineConfig",
     "GatedMLPSpec",
+    "GatedRecurrenceSpec",
     "LatentAttentionSpec",
     "LayerNormSpec",
     "LayerSpec",
@@ -58,9 +69,11 @@ __all__ = [
     "RotarySpec",
     "RoutedMLPSpec",
     "RunSpec",
+    "SandwichConvSpec",
     "SchedulerConfig",
     "StreamMixSpec",
     "TekilornConfig",
+    "ZabutarConfig",
     "ZofadraConfig",
     "architecture_of",
     "known_architectures",

@@ -32,6 +32,9 @@ class NormSpec:
     eps: float
     kind: str = "rmsnorm"
     rename: tuple = ()
+    # The checkpoint stores the weight's distance from this number: the rows are multiplied
+    # by ``weight_offset`` + stored weight (0: the weight is stored as it is used).
+    weight_offset: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -111,6 +114,14 @@ class AttentionSpec:
     head_gate: bool = False
     # None, or a DifferentialSpec: every head has two score maps over the same values.
     differential: object = None
+    # None, or (rows, far): a learned bias by distance and head, tensor ``rel`` [rows, heads].
+    # Distance n = i - j uses row n below rows/2 and beyond that rows that widen
+    # logarithmically: min(rows - 1, h + floor(ln(n / h) / ln(far / h) * (rows - h))), h = rows/2.
+    # The bias is added to the scaled score (the scale does not multiply it).
+    distance_bias_table: tuple | None = None
+    # False: the layer has no key and value projections; it reads another run's cache
+    # (``RunSpec.cache_of``) with queries, bias and output projection of its own.
+    kv_projection: bool = True
 
 
 @dataclass(frozen=True)
@@ -168,6 +179,37 @@ class LinearRecurrenceSpec:
 
 
 @dataclass(frozen=True)
+class GatedRecurrenceSpec:
+    """Linear attention whose forget gate also decides what is written: per head a state
+    S [head_dim, v_head_dim] with S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t,
+    q = silu(W_q x), v = W_v x and f = l + (1 - l) sigmoid(W_f x + b_f) for a learned lower
+    bound l per head and channel.  Each head's output is RMS-normalised over its values with
+    one weight vector shared by the heads, and the heads are projected by W_o."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    v_head_dim: int
+    norm_eps: float
+    kind: str = "gated_recurrence"
+    rename: tuple = ()
+
+
+@dataclass(frozen=True)
+class DenseMLPSpec:
+    """down(act(up(x) + b_up)) + b_down, no gate.  ``activation`` "xielu": with two learned
+    numbers p, q (tensor ``act`` [2]) act(z) = softplus(p) z^2 + z / 2 above zero and
+    (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 at and below it."""
+
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "xielu"
+    bias: bool = True
+    kind: str = "dense_mlp"
+    rename: tuple = ()
+
+
+@dataclass(frozen=True)
 class GatedMLPSpec:
     """down(act(gate(x)) * up(x)) without biases."""
 
@@ -203,6 +245,18 @@ class RoutedMLPSpec:
     shared_gate: bool = False
     kind: str = "routed_mlp"
     rename: tuple = ()
+    # The last ``identity`` outputs of the router (it has ``experts`` + ``identity``) stand
+    # for experts without tensors whose output is their input.
+    identity: int = 0
+    # True: tensor ``correction`` [router outputs] is added to the scores for the choice of
+    # experts only; the weights come from the scores without it.
+    correction: bool = False
+    # None, or (count, keep): the router's outputs form ``count`` equal groups of neighbours;
+    # a group's mark is its largest choice score and only the ``keep`` best groups can be chosen.
+    groups: tuple | None = None
+    # With ``renormalise``: weights = scores / (sum + renorm_floor); always times weight_scale.
+    renorm_floor: float = 0.0
+    weight_scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -235,6 +289,22 @@ class StreamMixSpec:
     streams: int = 1
     learned: bool = False
     update_scale: float = 1.0
+
+
+@dataclass(frozen=True)
+class SandwichConvSpec:
+    """Options of the "sandwich_conv" arrangement: every sublayer's update is normalised
+    again before it joins the residual stream (x += norm_b(sublayer(u))), and what a sublayer
+    reads is u = y + conv(y), y the normalised stream and conv a causal convolution over time
+    with ``taps`` taps per channel (tensors ``conv1`` / ``conv2`` [width, taps]; tap j weighs
+    the input taps - 1 - j tokens back).  The last taps - 1 rows of y belong to a request's
+    state, for both sublayers.  ``mixer_out_norm`` / ``ffn_out_norm``: the specs of the norms
+    norm_b (roles of the same names; the second is None for a layer without feed-forward)."""
+
+    taps: int
+    mixer_out_norm: object = None
+    ffn_out_norm: object = None
+    rename: tuple = ()
 
 
 @dataclass(frozen=True)
@@ -272,3 +342,6 @@ class ModelSpec:
     residual_streams: int = 1        # copies of the residual stream (see StreamMixSpec)
     # tensors of the checkpoint that belong to no layer: (name, shape, role) each
     extra_tensors: tuple = ()
+    # None, or the name of a tensor [max_positions, hidden]: row p is added to the embedding
+    # of the token at position p.
+    position_table_name: str | None = None

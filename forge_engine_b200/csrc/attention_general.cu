@@ -196,6 +196,8 @@ struct GeneralAttn {
   const int* positions;
   const int* token_entry;
   const float* slopes;      // per query head, or null: s -= slope * (pos - key)
+  const float* dist_bias;   // or null: [heads, dist_len], s += dist_bias[head, min(pos - key, dist_len - 1)]
+  int dist_len;
   int window;
   float scale;
   // What the plain layer does not have (all off when zero / null):
@@ -315,6 +317,8 @@ attention_general_kernel(GeneralAttn a, int* status) {
       float sc = s[r] * row_scale;
       if (a.softcap > 0.f) sc = a.softcap * tanhf(sc * inv_cap);
       sc = valid ? sc - slope[r] * dist : -INFINITY;
+      if (a.dist_bias != nullptr && valid && r < R)
+        sc += a.dist_bias[(size_t)(head0 + r) * a.dist_len + min(pos - key, a.dist_len - 1)];
       const float m_new = fmaxf(m[r], warp_max(sc));
       p[r] = valid ? expf(sc - m_new) : 0.f;
       const float corr = (m[r] == -INFINITY) ? 0.f : expf(m[r] - m_new);
@@ -430,7 +434,8 @@ FE_EXPORT int fe_attention_general(const void* q, long long q_token_stride, long
                                    int k_row, int k_dim, const void* v_cache, int v_row, int v_dim, void* out,
                                    long long o_token_stride, long long o_head_stride, int dtype, const int* block_table,
                                    int max_pages, int page_size, int num_pages, int num_kv_heads, int num_q_heads,
-                                   const int* positions, const int* token_entry, const float* slopes, int window,
+                                   const int* positions, const int* token_entry, const float* slopes,
+                                   const float* dist_bias, int dist_len, int window,
                                    float scale, int keep_first, float softcap, float temp_coef, int temp_every,
                                    int parts, long long q_part_stride, int k_part_stride, long long o_part_stride,
                                    const float* gate, long long gate_stride, int out_f32, int n_tokens, int* status,
@@ -439,10 +444,10 @@ FE_EXPORT int fe_attention_general(const void* q, long long q_token_stride, long
   if (parts < 1) parts = 1;
   if (num_kv_heads < 1 || num_q_heads % num_kv_heads || (long long)num_kv_heads * parts > 65535) return FE_ERR_BAD_SHAPE;
   if (k_dim < 1 || v_dim < 1 || k_part_stride * (parts - 1) + k_dim > k_row || v_dim > v_row) return FE_ERR_BAD_SHAPE;
-  if (keep_first < 0 || temp_every < 0 || softcap < 0.f) return FE_ERR_BAD_SHAPE;
+  if (keep_first < 0 || temp_every < 0 || softcap < 0.f || (dist_bias != nullptr && dist_len < 1)) return FE_ERR_BAD_SHAPE;
   GeneralAttn a{q, q_token_stride, q_head_stride, k_cache, k_row, k_dim, v_cache, v_row, v_dim, out, o_token_stride,
                 o_head_stride, block_table, max_pages, page_size, num_pages, num_kv_heads, num_q_heads, positions,
-                token_entry, slopes, window, scale, keep_first, softcap, temp_coef, temp_every, parts, q_part_stride,
+                token_entry, slopes, dist_bias, dist_len, window, scale, keep_first, softcap, temp_coef, temp_every, parts, q_part_stride,
                 k_part_stride, o_part_stride, gate, gate_stride, out_f32};
   if (dtype == FE_DTYPE_F32) return dispatch_general<float>(a, n_tokens, status, stream);
   if (dtype == FE_DTYPE_BF16) return dispatch_general<bf16>(a, n_tokens, status, stream);

@@ -49,7 +49,7 @@ struct Params {
   void* out; long long o_ts, o_hs;
   const int* table; int max_pages, page_size, num_pages, nkv, groups;
   const int* cu_tokens; const int* starts;
-  const float* slopes; int window; float scale;
+  const float* slopes; const float* dist_bias; int dist_len; int window; float scale;
   int splits; int tiles; float* part;
   // what the plain layer does not have (off when zero / null); see GeneralAttn in attention_general.cu
   int keep_first; float softcap, temp_coef; int temp_every;
@@ -173,6 +173,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
   const int quad = lane >> 2, pair = lane & 3;
   int row_pos[2];
   float row_slope[2], row_scale[2];
+  const float* row_bias[2];    // the row's head in the table of biases by distance, or null
   bool row_live[2];
   // scores are kept in units of log 2, so that exp is one exp2; with a cap the product is first
   // brought to units of the cap, and cap * log2(e) * tanh(.) is taken
@@ -184,6 +185,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
     row_live[h] = rho < rows_total;
     row_pos[h] = row_live[h] ? start + rho / p.groups : -1;
     row_slope[h] = (row_live[h] && p.slopes) ? p.slopes[kvh * p.groups + rho % p.groups] * LOG2E : 0.f;
+    row_bias[h] = (row_live[h] && p.dist_bias) ? p.dist_bias + (size_t)(kvh * p.groups + rho % p.groups) * p.dist_len : nullptr;
     const float natural = p.scale * query_temperature(max(row_pos[h], 0), p.temp_coef, p.temp_every);
     row_scale[h] = capped ? natural / p.softcap : natural * LOG2E;
   }
@@ -253,6 +255,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
           float sc = s[j][c] * row_scale[h];
           if (capped) sc = cap2 * tanh_capped(sc);
           sc -= row_slope[h] * (float)(row_pos[h] - key);
+          if (row_bias[h] != nullptr) sc = fmaf(row_bias[h][min(row_pos[h] - key, p.dist_len - 1)], LOG2E, sc);
           s[j][c] = sc;
           mx[h] = fmaxf(mx[h], sc);
         }
@@ -269,6 +272,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
           float sc = s[j][c] * row_scale[h];
           if (capped) sc = cap2 * tanh_capped(sc);
           sc = visible ? sc - row_slope[h] * (float)(row_pos[h] - key) : -INFINITY;
+          if (row_bias[h] != nullptr && visible) sc = fmaf(row_bias[h][min(row_pos[h] - key, p.dist_len - 1)], LOG2E, sc);
           s[j][c] = sc;
           mx[h] = fmaxf(mx[h], sc);
         }
@@ -429,7 +433,8 @@ FE_EXPORT int GM_NAME(fe_attention_gmma_)(const void* q, long long q_ts, long lo
                                           const void* v_cache, int v_row, void* out, long long o_ts, long long o_hs,
                                           const int* block_table, int max_pages, int page_size, int num_pages, int nkv,
                                           int num_q_heads, const int* cu_tokens, const int* starts, int entries,
-                                          int max_new, const float* slopes, int window, float scale, int splits,
+                                          int max_new, const float* slopes, const float* dist_bias, int dist_len,
+                                          int window, float scale, int splits,
                                           float* workspace, int keep_first, float softcap, float temp_coef,
                                           int temp_every, int parts, long long q_ps, int k_ps, long long o_ps,
                                           const float* gate, long long gate_stride, int out_f32, int row_hi, int* status,
@@ -437,6 +442,7 @@ FE_EXPORT int GM_NAME(fe_attention_gmma_)(const void* q, long long q_ts, long lo
   if (entries <= 0 || max_new <= 0) return 0;
   if (parts < 1) parts = 1;
   if (nkv < 1 || num_q_heads % nkv || (long long)nkv * parts > 65535 || entries > 65535) return FE_ERR_BAD_SHAPE;
+  if (dist_bias != nullptr && dist_len < 1) return FE_ERR_BAD_SHAPE;
   if (keep_first < 0 || temp_every < 0 || softcap < 0.f || k_ps * (parts - 1) + DK > k_row) return FE_ERR_BAD_SHAPE;
   if (k_row % 8 || v_row % 8 || q_ts % 8 || q_hs % 8 || o_ts % 2 || o_hs % 2 || q_ps % 8 || k_ps % 8 || o_ps % 2) return FE_ERR_BAD_ALIGN;
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16 || (uintptr_t)out % 4) return FE_ERR_BAD_ALIGN;
@@ -446,7 +452,7 @@ FE_EXPORT int GM_NAME(fe_attention_gmma_)(const void* q, long long q_ts, long lo
   const int groups = num_q_heads / nkv;
   const int tiles = (int)(((long long)max_new * groups + BM - 1) / BM);
   Params p{(const bf16*)q, q_ts, q_hs, (const bf16*)k_cache, k_row, (const bf16*)v_cache, v_row, out, o_ts, o_hs,
-           block_table, max_pages, page_size, num_pages, nkv, groups, cu_tokens, starts, slopes, window, scale,
+           block_table, max_pages, page_size, num_pages, nkv, groups, cu_tokens, starts, slopes, dist_bias, dist_len, window, scale,
            splits, tiles, workspace, keep_first, softcap, temp_coef, temp_every, parts, q_ps, k_ps, o_ps, gate,
            gate_stride, out_f32, row_hi};
   static bool configured = false;

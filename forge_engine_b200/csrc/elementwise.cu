@@ -7,11 +7,13 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------
-// embedding: residual[n, c, :] = float(table[ids[n], :]) * scale for each of `copies` streams
+// embedding: residual[n, c, :] = float(table[ids[n], :]) * scale for each of `copies` streams;
+// with a table of learned positions, row positions[n] of it is added (unscaled, in 32-bit)
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab, float scale, int copies,
+                                 const int* __restrict__ positions, const T* __restrict__ pos_table, int pos_rows,
                                  int* status) {
   pdl_trigger();
   pdl_wait();
@@ -24,22 +26,32 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     return;
   }
   const T* src = table + (size_t)id * hidden;
+  const T* place = nullptr;
+  if (pos_table != nullptr) {
+    const int pos = positions[row];
+    if (pos < 0 || pos >= pos_rows) {
+      if (threadIdx.x == 0) atomicOr(status, FE_STATUS_BAD_POSITION);
+    } else {
+      place = pos_table + (size_t)pos * hidden;
+    }
+  }
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float v = scale == 1.f ? to_float(src[i]) : to_float(src[i]) * scale;
+    float v = scale == 1.f ? to_float(src[i]) : to_float(src[i]) * scale;
+    if (place != nullptr) v += to_float(place[i]);
     for (int c = 0; c < copies; ++c) dst[(size_t)c * hidden + i] = v;
   }
 }
 
 FE_EXPORT int fe_embedding(const int* ids, const void* table, int table_dtype, float* out,
-                           int n, int hidden, int vocab, float scale, int copies, int* status,
-                           cudaStream_t stream) {
+                           int n, int hidden, int vocab, float scale, int copies, const int* positions,
+                           const void* pos_table, int pos_rows, int* status, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (copies < 1) return FE_ERR_BAD_SHAPE;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == FE_DTYPE_F32)
-    return fe_launch_dependent(embedding_kernel<float>, dim3(n), dim3(threads), 0, stream, ids, (const float*)table, out, hidden, vocab, scale, copies, status);
+    return fe_launch_dependent(embedding_kernel<float>, dim3(n), dim3(threads), 0, stream, ids, (const float*)table, out, hidden, vocab, scale, copies, positions, (const float*)pos_table, pos_rows, status);
   else if (table_dtype == FE_DTYPE_BF16)
-    return fe_launch_dependent(embedding_kernel<bf16>, dim3(n), dim3(threads), 0, stream, ids, (const bf16*)table, out, hidden, vocab, scale, copies, status);
+    return fe_launch_dependent(embedding_kernel<bf16>, dim3(n), dim3(threads), 0, stream, ids, (const bf16*)table, out, hidden, vocab, scale, copies, positions, (const bf16*)pos_table, pos_rows, status);
   else
     return FE_ERR_BAD_DTYPE;
   return fe_last_error();
@@ -279,4 +291,42 @@ FE_EXPORT int fe_silu_mul(const void* gate_up, void* out, int dtype, int rows, i
     return FE_ERR_BAD_DTYPE;
   }
   return fe_last_error();
+}
+
+// ---------------------------------------------------------------------------
+// bias_xielu: out[n, i] = act(x[n, i] + bias[i]) with the activation
+//   act(z) = a_pos z^2 + z / 2                 for z > 0
+//            a_neg (exp(z) - 1 - z) + z / 2    for z <= 0
+// taken in 32-bit of the projection's sums (bias 32-bit or null); one rounding on store.
+// ---------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+bias_xielu_kernel(const TI* __restrict__ x, const float* __restrict__ bias, TO* __restrict__ out, long long total,
+                  int width, float a_pos, float a_neg) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    float z = to_float(x[i]);
+    if (bias != nullptr) z += bias[(int)(i % width)];
+    const float half = 0.5f * z;
+    const float v = z > 0.f ? fmaf(a_pos * z, z, half) : fmaf(a_neg, expm1f(z) - z, half);
+    out[i] = from_float<TO>(v);
+  }
+}
+
+FE_EXPORT int fe_bias_xielu(const void* x, int x_dtype, const float* bias, void* out, int out_dtype, long long rows,
+                            int width, float a_pos, float a_neg, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (width < 1) return FE_ERR_BAD_SHAPE;
+  const long long total = rows * width;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  int rc = FE_ERR_BAD_DTYPE;
+#define XIELU(TI, TO) \
+  rc = fe_launch_dependent(bias_xielu_kernel<TI, TO>, dim3((unsigned)blocks), dim3(256), 0, stream, (const TI*)x, bias, (TO*)out, total, width, a_pos, a_neg)
+  if (x_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32) XIELU(float, float);
+  else if (x_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_BF16) XIELU(float, bf16);
+  else if (x_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_BF16) XIELU(bf16, bf16);
+#undef XIELU
+  return rc ? rc : fe_last_error();
 }

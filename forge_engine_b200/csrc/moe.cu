@@ -103,53 +103,97 @@ FE_EXPORT int fe_moe_logits(const void* x, int x_dtype, const float* w, float* o
 // ---------------------------------------------------------------------------
 // route
 // ---------------------------------------------------------------------------
+#define MOE_MAX_GROUPS 64
+
+// What the plain router does not have (all off when zero / null).
+struct MoeRouteExtras {
+  int identity;             // the router's last `identity` outputs stand for units that hand their input on;
+                            //   they all count as one expert, number `experts`, that has no tiles
+  const float* correction;  // [experts + identity] or null: added to the score for the choice only
+  int group_count;          // 0, or: the outputs form this many equal groups of neighbours, a group's
+  int group_keep;           //   mark is its largest choice score, and only the best group_keep can be chosen
+  float renorm_floor;       // with renormalise: weight = score / (sum of the chosen + renorm_floor)
+  float weight_scale;       // every weight is multiplied by this
+};
+
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, long long ld, int n_tokens, int experts, int top, int softmax_scores,
-                 int renormalise, int* __restrict__ slot_expert, float* __restrict__ slot_weight,
+                 int renormalise, MoeRouteExtras x, int* __restrict__ slot_expert, float* __restrict__ slot_weight,
                  int* __restrict__ slot_rank, int* __restrict__ counts) {
+  __shared__ float group_mark[4][MOE_MAX_GROUPS];
   pdl_trigger();
   pdl_wait();
-  const int lane = threadIdx.x & 31;
-  const int token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int token = blockIdx.x * (blockDim.x >> 5) + warp;
   if (token >= n_tokens) return;
+  const int outputs = experts + x.identity;
   const float* z = logits + (size_t)token * ld;
   float big = -INFINITY, norm = 1.f;
   if (softmax_scores) {
-    for (int e = lane; e < experts; e += 32) big = fmaxf(big, z[e]);
+    for (int e = lane; e < outputs; e += 32) big = fmaxf(big, z[e]);
     big = warp_max(big);
     float sum = 0.f;
-    for (int e = lane; e < experts; e += 32) sum += expf(z[e] - big);
+    for (int e = lane; e < outputs; e += 32) sum += expf(z[e] - big);
     norm = 1.f / warp_sum(sum);
   }
+  auto score_of = [&](int e) { return softmax_scores ? expf(z[e] - big) * norm : 1.f / (1.f + expf(-z[e])); };
+  auto choice_of = [&](int e) { return x.correction ? score_of(e) + x.correction[e] : score_of(e); };
+  const int per_group = x.group_count > 0 ? outputs / x.group_count : outputs;
+  if (x.group_count > 0) {
+    for (int g = 0; g < x.group_count; ++g) {
+      float mark = -INFINITY;
+      for (int e = g * per_group + lane; e < (g + 1) * per_group; e += 32) mark = fmaxf(mark, choice_of(e));
+      mark = warp_max(mark);
+      if (lane == 0) group_mark[warp][g] = mark;
+    }
+    __syncwarp();
+  }
+  // whether output e may be chosen: fewer than group_keep groups rank ahead of its own (ties: the lower index)
+  auto open_to_choice = [&](int e) {
+    if (x.group_count <= 0) return true;
+    const int g = e / per_group;
+    const float mine = group_mark[warp][g];
+    int ahead = 0;
+    for (int o = 0; o < x.group_count; ++o) {
+      const float other = group_mark[warp][o];
+      ahead += (other > mine || (other == mine && o < g)) ? 1 : 0;
+    }
+    return ahead < x.group_keep;
+  };
   int chosen[MOE_MAX_TOP];
   float weight[MOE_MAX_TOP];
   float total = 0.f;
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int best_e = 0x7fffffff;
-    for (int e = lane; e < experts; e += 32) {
+    for (int e = lane; e < outputs; e += 32) {
       bool taken = false;
       for (int j = 0; j < k; ++j) taken |= chosen[j] == e;
-      if (taken) continue;
-      const float score = softmax_scores ? expf(z[e] - big) * norm : 1.f / (1.f + expf(-z[e]));
-      if (score > best || (score == best && e < best_e)) { best = score; best_e = e; }
+      if (taken || !open_to_choice(e)) continue;
+      const float score = choice_of(e);
+      if (score > best || (score == best && e < best_e) || best_e == 0x7fffffff) { best = score; best_e = e; }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float other = __shfl_xor_sync(0xffffffffu, best, o);
       const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
-      if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
+      if (other_e != 0x7fffffff && (best_e == 0x7fffffff || other > best || (other == best && other_e < best_e))) {
+        best = other;
+        best_e = other_e;
+      }
     }
     chosen[k] = best_e;
-    weight[k] = best;
-    total += best;
+    // the weight comes from the score without the correction
+    weight[k] = x.correction ? score_of(min(best_e, outputs - 1)) : best;
+    total += weight[k];
   }
   if (lane == 0) {
     for (int k = 0; k < top; ++k) {
       const int slot = token * top + k;
-      slot_expert[slot] = chosen[k];
-      slot_weight[slot] = renormalise ? weight[k] / total : weight[k];
-      slot_rank[slot] = atomicAdd(&counts[chosen[k]], 1);
+      const int e = min(chosen[k], experts);       // every identity unit is expert number `experts`
+      slot_expert[slot] = e;
+      slot_weight[slot] = (renormalise ? weight[k] / (total + x.renorm_floor) : weight[k]) * x.weight_scale;
+      slot_rank[slot] = atomicAdd(&counts[e], 1);
     }
   }
 }
@@ -158,7 +202,7 @@ moe_route_kernel(const float* __restrict__ logits, long long ld, int n_tokens, i
 // plan
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024)
-moe_plan_kernel(int* __restrict__ counts, int experts, int slots, int max_tiles, int tile_rows, const int* __restrict__ slot_expert,
+moe_plan_kernel(int* __restrict__ counts, int experts, int tiled, int slots, int max_tiles, int tile_rows, const int* __restrict__ slot_expert,
                 const int* __restrict__ slot_rank, int* __restrict__ offsets, int* __restrict__ tile_expert,
                 int* __restrict__ tile_row, int* __restrict__ slot_row, int* __restrict__ row_slot) {
   extern __shared__ int start[];      // [experts + 1]
@@ -169,7 +213,8 @@ moe_plan_kernel(int* __restrict__ counts, int experts, int slots, int max_tiles,
     for (int e = 0; e < experts; ++e) {
       start[e] = at;
       const int count = counts[e];
-      for (int r = 0; r < count && tile < max_tiles; r += tile_rows, ++tile) {
+      // experts from `tiled` on (identity units) have rows but no products
+      for (int r = 0; e < tiled && r < count && tile < max_tiles; r += tile_rows, ++tile) {
         tile_expert[tile] = e;
         tile_row[tile] = at + r;
       }
@@ -471,7 +516,8 @@ template <typename TS, typename TO>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ slot_row, const float* __restrict__ slot_weight,
                    int top, int width, const TS* __restrict__ shared, const float* __restrict__ shared_logit,
-                   long long shared_ld, TO* __restrict__ out) {
+                   long long shared_ld, const int* __restrict__ slot_expert, int experts, const void* __restrict__ input,
+                   int input_bf16, TO* __restrict__ out) {
   pdl_trigger();
   pdl_wait();
   const int token = blockIdx.x;
@@ -484,7 +530,13 @@ moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ slot_
       for (int k = 0; k < top; ++k) {
         const int slot = token * top + k;
         float v[4];
-        load4(rows + (size_t)slot_row[slot] * width + c, v);
+        if (input != nullptr && slot_expert[slot] >= experts) {
+          // an identity unit: the row is the token's own input
+          if (input_bf16) load4((const bf16*)input + (size_t)token * width + c, v);
+          else load4((const float*)input + (size_t)token * width + c, v);
+        } else {
+          load4(rows + (size_t)slot_row[slot] * width + c, v);
+        }
         const float w = slot_weight ? slot_weight[slot] : 1.f;
 #pragma unroll
         for (int e = 0; e < 4; ++e) sum[e] += slot_weight ? v[e] * w : v[e];
@@ -503,7 +555,11 @@ moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ slot_
     float sum = 0.f;
     for (int k = 0; k < top; ++k) {
       const int slot = token * top + k;
-      const float v = rows[(size_t)slot_row[slot] * width + c];
+      float v;
+      if (input != nullptr && slot_expert[slot] >= experts)
+        v = input_bf16 ? to_float(((const bf16*)input)[(size_t)token * width + c]) : ((const float*)input)[(size_t)token * width + c];
+      else
+        v = rows[(size_t)slot_row[slot] * width + c];
       sum += slot_weight ? v * slot_weight[slot] : v;
     }
     if (shared != nullptr) sum = fmaf(gate, to_float(shared[(size_t)token * width + c]), sum);
@@ -521,23 +577,33 @@ FE_EXPORT int fe_moe_max_tiles(int slots, int experts, int tile_rows) {
   return (slots + tile_rows - 1) / tile_rows + (experts < slots ? experts : slots);
 }
 
-// logits [tokens, ld] (the first `experts` columns); counts [experts] must be zero and is zero
-// again afterwards; slot_* and row_slot [tokens * top]; offsets [experts + 1]; tile_* [max_tiles]
+// logits [tokens, ld] (the first `experts` + `identity` columns); counts [experts (+ 1 with identity
+// units)] must be zero and is zero again afterwards; slot_* and row_slot [tokens * top]; offsets
+// [experts + 1 (+ 1)]; tile_* [max_tiles]
 FE_EXPORT int fe_moe_route(const float* logits, long long ld, int n_tokens, int experts, int top, int softmax_scores,
                            int renormalise, int* counts, int* slot_expert, float* slot_weight, int* slot_rank,
                            int* slot_row, int* row_slot, int* offsets, int* tile_expert, int* tile_row, int max_tiles,
-                           int tile_rows, cudaStream_t stream) {
+                           int tile_rows, int identity, const float* correction, int group_count, int group_keep,
+                           float renorm_floor, float weight_scale, cudaStream_t stream) {
   if (tile_rows <= 0) tile_rows = MOE_BM;
   if (n_tokens <= 0) return 0;
-  if (experts < 1 || top < 1 || top > experts || top > MOE_MAX_TOP || ld < experts) return FE_ERR_BAD_SHAPE;
+  if (identity < 0) return FE_ERR_BAD_SHAPE;
+  const int outputs = experts + identity;
+  if (experts < 1 || top < 1 || top > outputs || top > MOE_MAX_TOP || ld < outputs) return FE_ERR_BAD_SHAPE;
+  if (group_count < 0 || group_count > MOE_MAX_GROUPS) return FE_ERR_BAD_SHAPE;
+  if (group_count > 0 && (outputs % group_count || group_keep < 1 || group_keep > group_count ||
+                          (long long)outputs / group_count * group_keep < top)) return FE_ERR_BAD_SHAPE;
   if ((long long)n_tokens * top > 0x7fffffffLL) return FE_ERR_TOO_LARGE;
-  if ((size_t)(experts + 1) * sizeof(int) > 160 * 1024) return FE_ERR_TOO_LARGE;
+  // with identity units the tables have one more expert: the one that stands for all of them
+  const int listed = experts + (identity > 0 ? 1 : 0);
+  if ((size_t)(listed + 1) * sizeof(int) > 160 * 1024) return FE_ERR_TOO_LARGE;
+  MoeRouteExtras extras{identity, correction, group_count, group_keep, renorm_floor, weight_scale};
   int rc = fe_launch_dependent(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, logits, ld, n_tokens,
-                               experts, top, softmax_scores, renormalise, slot_expert, slot_weight, slot_rank, counts);
+                               experts, top, softmax_scores, renormalise, extras, slot_expert, slot_weight, slot_rank, counts);
   if (rc) return rc;
-  const size_t smem = (size_t)(experts + 1) * sizeof(int);
+  const size_t smem = (size_t)(listed + 1) * sizeof(int);
   if (smem > 48 * 1024) cudaFuncSetAttribute(moe_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  rc = fe_launch_dependent(moe_plan_kernel, dim3(1), dim3(1024), smem, stream, counts, experts, n_tokens * top, max_tiles, tile_rows,
+  rc = fe_launch_dependent(moe_plan_kernel, dim3(1), dim3(1024), smem, stream, counts, listed, experts, n_tokens * top, max_tiles, tile_rows,
                            (const int*)slot_expert, (const int*)slot_rank, offsets, tile_expert, tile_row, slot_row, row_slot);
   return rc ? rc : fe_last_error();
 }
@@ -580,15 +646,19 @@ FE_EXPORT int fe_moe_grouped(const void* a, int a_dtype, long long lda, const vo
 
 FE_EXPORT int fe_moe_combine(const float* rows, const int* slot_row, const float* slot_weight, int top, int width,
                              const void* shared, int shared_dtype, const float* shared_logit, long long shared_ld,
-                             void* out, int out_dtype, int n_tokens, cudaStream_t stream) {
+                             void* out, int out_dtype, int n_tokens, const int* slot_expert, int experts,
+                             const void* input, int input_dtype, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
+  if (input != nullptr && (slot_expert == nullptr || (input_dtype != FE_DTYPE_F32 && input_dtype != FE_DTYPE_BF16)))
+    return FE_ERR_BAD_DTYPE;
+  const int input_bf16 = input_dtype == FE_DTYPE_BF16 ? 1 : 0;
   int pieces = (width & 3) == 0 ? (width / 4 + 255) / 256 : (width + 255) / 256;
   if (pieces > 32) pieces = 32;
   dim3 grid(n_tokens, pieces);
   int rc = FE_ERR_BAD_DTYPE;
 #define MOE_COMBINE(TS, TO)                                                                                           \
   rc = fe_launch_dependent(moe_combine_kernel<TS, TO>, grid, dim3(256), 0, stream, rows, slot_row, slot_weight, top, \
-                           width, (const TS*)shared, shared_logit, shared_ld, (TO*)out)
+                           width, (const TS*)shared, shared_logit, shared_ld, slot_expert, experts, input, input_bf16, (TO*)out)
   if (shared == nullptr) shared_dtype = FE_DTYPE_F32;
   if (shared_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32) MOE_COMBINE(float, float);
   else if (shared_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_BF16) MOE_COMBINE(float, bf16);

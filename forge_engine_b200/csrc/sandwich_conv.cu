@@ -1,0 +1,173 @@
+// Kernels of the block arrangement that normalises a sublayer's update before it joins the
+// residual stream and lets every sublayer read its input through a short causal convolution.
+//
+//   add_normed_rmsnorm  one block per row: x = residual + update * rsqrt(mean(update^2) + eps) * w_update
+//                       (written back unless told otherwise), out = x * rsqrt(mean(x^2) + eps) * w.
+//                       Both norms and the sum are 32-bit; one rounding on store.  With a row map
+//                       only the mapped rows are produced (the model's last norm on wanted rows).
+//   causal_conv_state   u_t = y_t + sum_j w[:, j] * y_(t - taps + 1 + j) per channel, over the tokens
+//                       of every entry of the step.  The taps - 1 rows of y before an entry's first
+//                       token come from the request's state row (zeros at a sequence's start), and
+//                       the step's last taps - 1 rows are left there for the next step.  Tokens
+//                       that read the state (an entry's first taps - 1) and the state's update are
+//                       the work of one block per entry, so no block reads a state row that
+//                       another writes; every other token has a block of its own that reads y alone.
+//                       A token's result depends on the taps rows themselves only, never on how the
+//                       sequence was cut into steps.
+#include "common.cuh"
+
+#define CONV_MAX_TAPS 8
+
+template <typename TU, typename TO>
+__global__ void __launch_bounds__(256)
+add_normed_rmsnorm_kernel(float* __restrict__ residual, const TU* __restrict__ update, const float* __restrict__ w_update,
+                          const float* __restrict__ weight, TO* __restrict__ out, const int* __restrict__ row_map, int size,
+                          float eps_update, float eps, int write_residual) {
+  extern __shared__ float row[];       // [size]
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = row_map ? row_map[r] : r;
+  float* res = residual + (size_t)src * size;
+  float ss = 0.f;
+  if (update != nullptr) {
+    const TU* upd = update + (size_t)src * size;
+    float su = 0.f;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+      const float u = to_float(upd[i]);
+      row[i] = u;
+      su = fmaf(u, u, su);
+    }
+    const float inv_u = 1.f / sqrtf(block_sum(su, scratch) / (float)size + eps_update);
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+      const float x = res[i] + row[i] * inv_u * w_update[i];
+      row[i] = x;
+      if (write_residual) res[i] = x;
+      ss = fmaf(x, x, ss);
+    }
+  } else {
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+      const float x = res[i];
+      row[i] = x;
+      ss = fmaf(x, x, ss);
+    }
+  }
+  const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)size + eps);
+  TO* dst = out + (size_t)r * size;
+  for (int i = threadIdx.x; i < size; i += blockDim.x) dst[i] = from_float<TO>(row[i] * inv * weight[i]);
+}
+
+// residual 32-bit [*, size]; update [*, size] or null; w_update, weight 32-bit [size] (as they
+// multiply: any offset of a stored weight is already in them); out [rows, size]
+FE_EXPORT int fe_add_normed_rmsnorm(float* residual, const void* update, int update_dtype, const float* w_update,
+                                    const float* weight, void* out, int out_dtype, const int* row_map, int rows, int size,
+                                    float eps_update, float eps, int write_residual, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (size < 1) return FE_ERR_BAD_SHAPE;
+  const size_t smem = (size_t)size * sizeof(float);
+  if (smem > 200 * 1024) return FE_ERR_TOO_LARGE;
+  int threads = 64;
+  while (threads < 256 && threads * 4 < size) threads <<= 1;
+  int rc = FE_ERR_BAD_DTYPE;
+#define LAUNCH(TU, TO)                                                                                                 \
+  do {                                                                                                                 \
+    if (smem > 48 * 1024)                                                                                              \
+      cudaFuncSetAttribute(add_normed_rmsnorm_kernel<TU, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    rc = fe_launch_dependent(add_normed_rmsnorm_kernel<TU, TO>, dim3(rows), dim3(threads), smem, stream, residual,     \
+                             (const TU*)update, w_update, weight, (TO*)out, row_map, size, eps_update, eps,            \
+                             write_residual);                                                                          \
+  } while (0)
+  if (update == nullptr) update_dtype = FE_DTYPE_F32;
+  if (update_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32) LAUNCH(float, float);
+  else if (update_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_BF16) LAUNCH(float, bf16);
+  else if (update_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_F32) LAUNCH(bf16, float);
+  else if (update_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_BF16) LAUNCH(bf16, bf16);
+#undef LAUNCH
+  return rc ? rc : fe_last_error();
+}
+
+// y 32-bit [tokens, width]; w 32-bit [taps, width] (tap j weighs the row taps - 1 - j tokens
+// back); state 32-bit, row `slot` at state + slot * state_stride holds [taps - 1, width], oldest
+// row first; out [tokens, width].
+template <typename TO>
+__global__ void __launch_bounds__(256)
+causal_conv_state_kernel(const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ state,
+                         long long state_stride, const int* __restrict__ slots, const int* __restrict__ cu_tokens,
+                         const int* __restrict__ token_entry, TO* __restrict__ out, int n_tokens, int width, int taps) {
+  pdl_trigger();
+  pdl_wait();
+  const int back = taps - 1;
+  if ((int)blockIdx.x < n_tokens) {
+    // a token with all its taps inside the step
+    const int t = blockIdx.x;
+    const int first = cu_tokens[token_entry[t]];
+    if (t - first < back) return;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < CONV_MAX_TAPS; ++j)
+        if (j < taps) sum = fmaf(w[(size_t)j * width + c], y[(size_t)(t - back + j) * width + c], sum);
+      out[(size_t)t * width + c] = from_float<TO>(y[(size_t)t * width + c] + sum);
+    }
+    return;
+  }
+  // an entry's edge: its first taps - 1 tokens, then the state for the next step
+  const int entry = blockIdx.x - n_tokens;
+  const int first = cu_tokens[entry], count = cu_tokens[entry + 1] - first;
+  if (count <= 0 || back <= 0) return;
+  float* st = state + (size_t)slots[entry] * state_stride;
+  const int edge = min(count, back);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    // hist[k], k < back: the state's rows; hist[back + i]: y of the entry's token i (i < edge)
+    float hist[2 * CONV_MAX_TAPS];
+    float wc[CONV_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+      wc[j] = j < taps ? w[(size_t)j * width + c] : 0.f;
+      hist[j] = j < back ? st[(size_t)j * width + c] : 0.f;
+      hist[CONV_MAX_TAPS + j] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < CONV_MAX_TAPS; ++i)
+      if (i < edge) hist[back + i] = y[(size_t)(first + i) * width + c];
+#pragma unroll
+    for (int i = 0; i < CONV_MAX_TAPS; ++i) {
+      if (i < edge) {
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; ++j)
+          if (j < taps) sum = fmaf(wc[j], hist[i + j], sum);
+        out[(size_t)(first + i) * width + c] = from_float<TO>(hist[back + i] + sum);
+      }
+    }
+    // the last taps - 1 rows of (state rows, the step's y rows)
+#pragma unroll
+    for (int k = 0; k < CONV_MAX_TAPS; ++k) {
+      if (k < back) {
+        const int at = count + k;          // index into that sequence
+        st[(size_t)k * width + c] = at < back + edge ? hist[at] : y[(size_t)(first + at - back) * width + c];
+      }
+    }
+  }
+}
+
+FE_EXPORT int fe_causal_conv_state(const float* y, const float* w, float* state, long long state_stride, const int* slots,
+                                   const int* cu_tokens, const int* token_entry, void* out, int out_dtype, int n_tokens,
+                                   int n_entries, int width, int taps, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (taps < 1 || taps > CONV_MAX_TAPS || width < 1) return FE_ERR_BAD_SHAPE;
+  if (taps > 1 && state == nullptr) return FE_ERR_BAD_SHAPE;
+  int threads = 64;
+  while (threads < 256 && threads < width) threads <<= 1;
+  const dim3 grid(n_tokens + (taps > 1 ? n_entries : 0));
+  int rc;
+  if (out_dtype == FE_DTYPE_F32)
+    rc = fe_launch_dependent(causal_conv_state_kernel<float>, grid, dim3(threads), 0, stream, y, w, state, state_stride,
+                             slots, cu_tokens, token_entry, (float*)out, n_tokens, width, taps);
+  else if (out_dtype == FE_DTYPE_BF16)
+    rc = fe_launch_dependent(causal_conv_state_kernel<bf16>, grid, dim3(threads), 0, stream, y, w, state, state_stride,
+                             slots, cu_tokens, token_entry, (bf16*)out, n_tokens, width, taps);
+  else return FE_ERR_BAD_DTYPE;
+  return rc ? rc : fe_last_error();
+}

@@ -36,6 +36,8 @@ def expected_tensors(spec: ModelSpec) -> dict:
                 out[join_name(prefix, local)] = info
     for name, shape, role in getattr(spec, "extra_tensors", ()):
         out[name] = WeightInfo(tuple(shape), role)
+    if getattr(spec, "position_table_name", None):
+        out[spec.position_table_name] = WeightInfo((spec.max_positions, spec.hidden_size))
     if not spec.tie_embeddings:
         out[spec.head_name] = WeightInfo((spec.vocab_size, spec.hidden_size))
     return out
@@ -66,6 +68,10 @@ class DecoderModel:
         self.spec = spec
         self.ctx = ctx
         self.embed = weights[spec.embed_name].contiguous()
+        # learned absolute positions: row p joins the embedding of the token at position p
+        self.position_table = None
+        if getattr(spec, "position_table_name", None):
+            self.position_table = weights[spec.position_table_name].to(self.embed.dtype).contiguous()
         self.blocks = []
         for layer in spec.layers:
             block_cls = arrangement_class(layer.arrangement)
@@ -152,7 +158,8 @@ class DecoderModel:
         h = torch.empty(shape, dtype=torch.float32, device=self.ctx.device)
         with self.ctx.section("embedding"):
             native.embedding(batch.token_ids, self.embed, h, self.ctx.status,
-                             scale=getattr(self.spec, "embedding_scale", 1.0))
+                             scale=getattr(self.spec, "embedding_scale", 1.0), positions=batch.positions,
+                             position_table=self.position_table)
         pending = None
         for index, run in enumerate(self.spec.schedule):
             shift = getattr(run, "shift", None)

@@ -56,18 +56,22 @@ def lib() -> ctypes.CDLL:
 def _declare(handle: ctypes.CDLL) -> None:
     p, i, f, ll = c_void_p, c_int, c_float, ctypes.c_longlong
     signatures = {
-        "fe_embedding": [p, p, i, p, i, i, i, f, i, p, p],
+        "fe_embedding": [p, p, i, p, i, i, i, f, i, p, p, i, p, p],
         "fe_stream_mix_norm": [p, i, p, i, f, p, p, p, i, p, f, p, i, p, i, i, i, p],
         "fe_act_mul": [p, i, p, i, i, i, i, i, f, f, p],
         "fe_gated_rmsnorm": [p, p, i, i, p, p, i, i, i, f, p],
         "fe_qkv_prepare": [p, i, i, i, i, i, i, p, i, p, i, i, i, i, i, p, i, p, i, i, i, f, p, i, i, p, ll, ll, i,
                            p, p, i, p, i, i, i, p, p, i, p, p],
-        "fe_attention_general": [p, ll, ll, p, i, i, p, i, i, p, ll, ll, i, p, i, i, i, i, i, p, p, p, i, f,
+        "fe_attention_general": [p, ll, ll, p, i, i, p, i, i, p, ll, ll, i, p, i, i, i, i, i, p, p, p, p, i, i, f,
                                  i, f, f, i, i, ll, i, ll, p, ll, i, i, p, p],
         "fe_differential_combine": [p, p, i, ll, i, f, f, f, p],
-        "fe_moe_route": [p, ll, i, i, i, i, i, p, p, p, p, p, p, p, p, p, i, i, p],
+        "fe_bias_xielu": [p, i, p, p, i, ll, i, f, f, p],
+        "fe_gated_recurrence": [p, ll, i, i, i, p, p, p, f, p, i, p, p, p, i, i, i, i, i, p, p],
+        "fe_add_normed_rmsnorm": [p, p, i, p, p, p, i, p, i, i, f, f, i, p],
+        "fe_causal_conv_state": [p, p, p, ll, p, p, p, p, i, i, i, i, i, p],
+        "fe_moe_route": [p, ll, i, i, i, i, i, p, p, p, p, p, p, p, p, p, i, i, i, p, i, i, f, f, p],
         "fe_moe_grouped": [p, i, ll, p, p, i, p, i, i, i, i, i, p, p, p, p, p, i, f, f, i, p],
-        "fe_moe_combine": [p, p, p, i, i, p, i, p, ll, p, i, i, p],
+        "fe_moe_combine": [p, p, p, i, i, p, i, p, ll, p, i, i, p, i, p, i, p],
         "fe_moe_max_tiles": [i, i, i],
         "fe_linear_recurrence": [p, i, i, i, i, i, i, p, p, p, p, p, i, i, i, i, i, p],
         "fe_linear_recurrence_chunked": [p, i, i, i, i, i, i, p, p, p, p, p, p, i, i, i, i, i, i, p],
@@ -291,17 +295,25 @@ def _dense(t: torch.Tensor, name: str) -> torch.Tensor:
 
 
 def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
-              scale: float = 1.0) -> None:
+              scale: float = 1.0, positions: torch.Tensor | None = None, position_table: torch.Tensor | None = None) -> None:
     """out[n] = float(table[ids[n]]) * scale; out is the 32-bit residual stream [N, H], or
-    [N, S, H] for S copies of it (every copy gets the same row)."""
+    [N, S, H] for S copies of it (every copy gets the same row).  With ``position_table``
+    [places, H] (dtype of ``table``) row ``positions[n]`` of it is added, unscaled."""
     _dense(ids, "ids"), _dense(table, "table"), _dense(out, "out")
     assert ids.dtype == torch.int32 and out.dtype == torch.float32
     n, hidden = out.shape[0], out.shape[-1]
     copies = out.shape[1] if out.dim() == 3 else 1
     assert table.shape[1] == hidden
+    places = 0
+    if position_table is not None:
+        _dense(position_table, "position_table")
+        assert position_table.dtype == table.dtype and position_table.shape[1] == hidden
+        assert positions is not None and positions.dtype == torch.int32 and positions.numel() == n
+        places = position_table.shape[0]
     check(
         lib().fe_embedding(ptr(ids), ptr(table), code(table), ptr(out), n, hidden, table.shape[0],
-                           float(scale), int(copies), ptr(status), stream()),
+                           float(scale), int(copies), ptr(positions) if position_table is not None else None,
+                           ptr(position_table), int(places), ptr(status), stream()),
         "embedding",
     )
 
@@ -426,19 +438,31 @@ def gemm_tc5_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilog
 
 
 def moe_route(logits: torch.Tensor, experts: int, top: int, softmax: bool, renormalise: bool, counts: torch.Tensor,
-              ints: torch.Tensor, slot_weight: torch.Tensor, max_tiles: int, tile_rows: int = 0) -> dict:
+              ints: torch.Tensor, slot_weight: torch.Tensor, max_tiles: int, tile_rows: int = 0, *,
+              identity: int = 0, correction: torch.Tensor | None = None, groups: tuple | None = None,
+              renorm_floor: float = 0.0, weight_scale: float = 1.0) -> dict:
     """Choose ``top`` of ``experts`` per token from 32-bit ``logits`` [N, >= experts] and lay
-    the (token, choice) slots out by expert.  ``counts`` int32 [experts] must be zero (it is
-    zero again afterwards); ``ints`` is int32 scratch of at least 4 * N * top + experts + 1 +
-    2 * max_tiles elements.  Returns views of it by name."""
+    the (token, choice) slots out by expert.  ``counts`` int32 [experts + 1] must be zero (it is
+    zero again afterwards); ``ints`` is int32 scratch of at least 4 * N * top + experts + 2 +
+    2 * max_tiles elements.  Returns views of it by name.
+
+    ``identity``: the router has that many outputs more, for units that hand their input on;
+    a slot that chose one gets expert number ``experts`` (rows, but no tiles).  ``correction``
+    (32-bit [experts + identity]) is added to the scores for the choice only.  ``groups``
+    (count, keep): the outputs form ``count`` equal groups of neighbours and only those of the
+    ``keep`` groups with the largest choice score can be chosen.  Weights are the chosen scores
+    (divided by their sum + ``renorm_floor`` with ``renormalise``) times ``weight_scale``."""
     n = logits.shape[0]
     slots = n * top
-    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= experts
-    assert counts.dtype == torch.int32 and counts.numel() >= experts and ints.dtype == torch.int32
+    outputs = experts + int(identity)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= outputs
+    assert counts.dtype == torch.int32 and counts.numel() >= experts + 1 and ints.dtype == torch.int32
     assert slot_weight.dtype == torch.float32 and slot_weight.numel() >= slots
-    assert ints.numel() >= 4 * slots + experts + 1 + 2 * max_tiles
+    assert ints.numel() >= 4 * slots + experts + 2 + 2 * max_tiles
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == outputs and correction.is_cuda)
+    group_count, group_keep = groups or (0, 0)
     names = (("slot_expert", slots), ("slot_rank", slots), ("slot_row", slots), ("row_slot", slots),
-             ("offsets", experts + 1), ("tile_expert", max_tiles), ("tile_row", max_tiles))
+             ("offsets", experts + 2), ("tile_expert", max_tiles), ("tile_row", max_tiles))
     views, at = {}, 0
     for name, count in names:
         views[name] = ints[at : at + count]
@@ -447,7 +471,8 @@ def moe_route(logits: torch.Tensor, experts: int, top: int, softmax: bool, renor
                              int(top), 1 if softmax else 0, 1 if renormalise else 0, ptr(counts),
                              ptr(views["slot_expert"]), ptr(slot_weight), ptr(views["slot_rank"]), ptr(views["slot_row"]),
                              ptr(views["row_slot"]), ptr(views["offsets"]), ptr(views["tile_expert"]),
-                             ptr(views["tile_row"]), int(max_tiles), int(tile_rows), stream()), "moe_route")
+                             ptr(views["tile_row"]), int(max_tiles), int(tile_rows), int(identity), ptr(correction),
+                             int(group_count), int(group_keep), float(renorm_floor), float(weight_scale), stream()), "moe_route")
     global LAUNCHES
     LAUNCHES += 1
     return views
@@ -473,18 +498,103 @@ def moe_grouped(a: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor | None, out:
 
 
 def moe_combine(rows: torch.Tensor, plan: dict, top: int, out: torch.Tensor, *, slot_weight: torch.Tensor | None = None,
-                shared: torch.Tensor | None = None, shared_logit: torch.Tensor | None = None) -> None:
+                shared: torch.Tensor | None = None, shared_logit: torch.Tensor | None = None,
+                identity_input: torch.Tensor | None = None, experts: int = 0) -> None:
     """out[token] = sum over the token's slots of rows[slot's row] (times ``slot_weight``) +
-    sigmoid(shared_logit[token]) * shared[token] (the gate 1 without a logit); 32-bit sums."""
+    sigmoid(shared_logit[token]) * shared[token] (the gate 1 without a logit); 32-bit sums.
+    With ``identity_input`` [N, width] a slot whose expert number is ``experts`` or above
+    contributes the token's row of it instead of a row of ``rows``."""
     _dense(rows, "rows"), _dense(out, "out")
     n, width = out.shape
     assert rows.dtype == torch.float32 and rows.shape == (n * top, width)
     assert shared is None or (shared.shape == out.shape and shared.is_contiguous())
     assert shared_logit is None or (shared_logit.dtype == torch.float32 and shared_logit.shape[0] == n)
+    assert identity_input is None or (identity_input.shape == out.shape and identity_input.is_contiguous())
     check(lib().fe_moe_combine(ptr(rows), ptr(plan["slot_row"]), ptr(slot_weight), int(top), int(width), ptr(shared),
                                code(shared) if shared is not None else F32, ptr(shared_logit),
                                int(shared_logit.stride(0)) if shared_logit is not None and n > 1 else 1,
-                               ptr(out), code(out), n, stream()), "moe_combine")
+                               ptr(out), code(out), n, ptr(plan["slot_expert"]), int(experts), ptr(identity_input),
+                               code(identity_input) if identity_input is not None else F32, stream()), "moe_combine")
+
+
+CONV_MAX_TAPS = 8      # what causal_conv_state takes
+
+
+def bias_xielu(x: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, a_pos: float, a_neg: float) -> None:
+    """out = act(x + bias), act(z) = a_pos z^2 + z / 2 above zero and a_neg (exp(z) - 1 - z) + z / 2
+    at and below it; taken in 32-bit, one rounding on store.  ``bias`` 32-bit [C] or None."""
+    _dense(x, "x"), _dense(out, "out")
+    rows, width = x.shape
+    assert out.shape == x.shape and (bias is None or (bias.dtype == torch.float32 and bias.numel() == width))
+    check(lib().fe_bias_xielu(ptr(x), code(x), ptr(bias), ptr(out), code(out), rows, width, float(a_pos), float(a_neg),
+                              stream()), "bias_xielu")
+
+
+def gated_recurrence(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_bias: torch.Tensor | None,
+                     lower: torch.Tensor, norm_weight: torch.Tensor, eps: float, state: torch.Tensor,
+                     slots: torch.Tensor, cu_tokens: torch.Tensor, out: torch.Tensor, n_entries: int,
+                     status: torch.Tensor) -> None:
+    """The gated linear recurrence over the tokens of every entry, from and to the request's
+    state row.  ``proj`` 32-bit [N, C] holds the sums of the q, f and v projections from
+    columns ``q_off``, ``f_off`` and ``v_off`` on (heads x dk, heads x dk, heads x dv);
+    q = silu(zq), f = lower + (1 - lower) sigmoid(zf + f_bias); ``state`` 32-bit
+    [rows, heads, dk, dv]: S <- diag(f) S + (1 - f) v^T, o = S^T q, and ``out`` [N, heads * dv]
+    gets o / sqrt(mean_over_dv(o^2) + eps) * norm_weight per head."""
+    _dense(proj, "proj"), _dense(state, "state"), _dense(out, "out")
+    rows, heads, dk, dv = state.shape
+    assert proj.dtype == torch.float32 and state.dtype == torch.float32
+    assert lower.dtype == torch.float32 and lower.numel() == heads * dk and lower.is_contiguous()
+    assert f_bias is None or (f_bias.dtype == torch.float32 and f_bias.numel() == heads * dk and f_bias.is_contiguous())
+    assert norm_weight.dtype == torch.float32 and norm_weight.numel() == dv
+    assert out.shape == (proj.shape[0], heads * dv) and slots.dtype == torch.int32 and cu_tokens.dtype == torch.int32
+    assert max(q_off, f_off) + heads * dk <= proj.shape[1] and v_off + heads * dv <= proj.shape[1]
+    check(lib().fe_gated_recurrence(ptr(proj), int(proj.shape[1]), int(q_off), int(f_off), int(v_off), ptr(f_bias),
+                                    ptr(lower), ptr(norm_weight), float(eps), ptr(state), int(rows), ptr(slots),
+                                    ptr(cu_tokens), ptr(out), code(out), int(n_entries), int(heads), int(dk), int(dv),
+                                    ptr(status), stream()), "gated_recurrence")
+
+
+def add_normed_rmsnorm(residual: torch.Tensor, update: torch.Tensor | None, update_weight: torch.Tensor | None,
+                       weight: torch.Tensor, out: torch.Tensor, eps_update: float, eps: float,
+                       row_map: torch.Tensor | None = None, write_residual: bool = True) -> None:
+    """residual (32-bit [N, C]) += update / sqrt(mean(update^2) + eps_update) * update_weight,
+    then out = residual / sqrt(mean(residual^2) + eps) * weight; both weights 32-bit as they
+    multiply.  Without ``update`` only the second norm runs.  With ``row_map`` only those rows
+    are produced (``write_residual`` False leaves the stream as it was)."""
+    _dense(residual, "residual"), _dense(out, "out")
+    size = residual.shape[-1]
+    rows = residual.shape[0] if row_map is None else row_map.numel()
+    assert residual.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == size
+    assert out.shape == (rows, size)
+    if update is not None:
+        _dense(update, "update")
+        assert update.shape == residual.shape and update_weight is not None
+        assert update_weight.dtype == torch.float32 and update_weight.numel() == size
+    check(lib().fe_add_normed_rmsnorm(ptr(residual), ptr(update), code(update) if update is not None else F32,
+                                      ptr(update_weight), ptr(weight), ptr(out), code(out), ptr(row_map), int(rows),
+                                      int(size), float(eps_update), float(eps), 1 if write_residual else 0, stream()),
+          "add_normed_rmsnorm")
+
+
+def causal_conv_state(y: torch.Tensor, taps_weight: torch.Tensor, state: torch.Tensor | None, slots: torch.Tensor,
+                      cu_tokens: torch.Tensor, token_entry: torch.Tensor, out: torch.Tensor, n_entries: int) -> None:
+    """out_t = y_t + sum_j w[j] * y_(t - taps + 1 + j) per channel over every entry's tokens.
+    ``y`` 32-bit [N, C]; ``taps_weight`` 32-bit [taps, C]; ``state`` 32-bit, row ``slot`` (its
+    first extent) holds the request's last taps - 1 rows of y, oldest first, read at an
+    entry's start and left for the next step."""
+    _dense(y, "y"), _dense(out, "out"), _dense(taps_weight, "taps_weight")
+    n, width = y.shape
+    taps = taps_weight.shape[0]
+    assert y.dtype == torch.float32 and taps_weight.dtype == torch.float32 and taps_weight.shape[1] == width
+    assert out.shape == y.shape
+    stride = 0
+    if taps > 1:
+        assert state is not None and state.dtype == torch.float32 and state[0].is_contiguous()
+        assert state[0].numel() == (taps - 1) * width
+        stride = int(state.stride(0))
+    check(lib().fe_causal_conv_state(ptr(y), ptr(taps_weight), ptr(state), stride, ptr(slots), ptr(cu_tokens),
+                                     ptr(token_entry), ptr(out), code(out), int(n), int(n_entries), int(width), int(taps),
+                                     stream()), "causal_conv_state")
 
 
 def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float) -> None:
@@ -593,7 +703,7 @@ def general_attention_lib(key_dim: int, value_dim: int, value_in_key: bool):
         suffix = f"{key_dim}_{value_dim}_{1 if value_in_key else 0}"
         run = getattr(handle, f"fe_attention_gmma_{suffix}")
         p, i, f, ll = c_void_p, c_int, c_float, ctypes.c_longlong
-        run.argtypes = [p, ll, ll, p, i, p, i, p, ll, ll, p, i, i, i, i, i, p, p, i, i, p, i, f, i, p,
+        run.argtypes = [p, ll, ll, p, i, p, i, p, ll, ll, p, i, i, i, i, i, p, p, i, i, p, p, i, i, f, i, p,
                         i, f, f, i, i, ll, i, ll, p, ll, i, i, p, p]
         run.restype = c_int
         space = getattr(handle, f"fe_attention_gmma_workspace_{suffix}")
@@ -653,6 +763,7 @@ def attention_general(
     part_strides: tuple = (0, 0, 0),
     gate: torch.Tensor | None = None,
     row_hi: int = 0,
+    distance_bias: torch.Tensor | None = None,
 ) -> None:
     """Paged causal attention for any key and value size: scores, softmax and sums in 32-bit.
 
@@ -665,7 +776,8 @@ def attention_general(
     is the first ``k_dim`` elements of a row, the value the first ``v_dim`` of ``v_cache``'s
     row (``v_cache`` may be ``k_cache`` itself: one cached vector that is key and value).
     ``slopes`` (per query head, 32-bit) takes slope * (query position - key position) off
-    every score; ``window`` keeps the query's own and the window - 1 keys before it, and with
+    every score; ``distance_bias`` (32-bit [heads, L]) adds entry [head, min(distance, L - 1)] to
+    every (scaled, capped) score; ``window`` keeps the query's own and the window - 1 keys before it, and with
     ``keep_first`` the keys at positions below it as well.  ``softcap`` c: scores become
     c tanh(score / c); ``query_temperature`` (coef, every): a query at position p has its
     scores multiplied by 1 + coef ln(floor((p + 1) / every) + 1).  ``parts`` > 1: every head has
@@ -682,6 +794,9 @@ def attention_general(
     assert q.dtype == k_cache.dtype == v_cache.dtype and out.dtype in (q.dtype, torch.float32)
     assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == num_q_heads and slopes.is_cuda)
     assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == n and gate.shape[1] >= num_q_heads)
+    assert distance_bias is None or (distance_bias.dtype == torch.float32 and distance_bias.is_cuda and distance_bias.is_contiguous()
+                                     and distance_bias.dim() == 2 and distance_bias.shape[0] == num_q_heads)
+    dist_len = 0 if distance_bias is None else int(distance_bias.shape[1])
     out_f32 = 1 if out.dtype == torch.float32 and q.dtype != torch.float32 else 0
     coef, every = query_temperature or (0.0, 0)
     gate_stride = 0 if gate is None else (int(gate.stride(0)) if n > 1 else int(gate.shape[1]))
@@ -701,7 +816,7 @@ def attention_general(
             run(ptr(q), int(q_strides[0]), int(q_strides[1]), ptr(k_cache), k_row, ptr(v_cache), v_row, ptr(out),
                 int(o_strides[0]), int(o_strides[1]), ptr(block_table), block_table.shape[1], page_size, num_pages, nkv,
                 int(num_q_heads), ptr(cu_tokens), ptr(starts), int(n_entries), int(max_new), ptr(slopes),
-                int(window or 0), float(scale), int(splits), ptr(workspace), *extras, int(row_hi), ptr(status), stream()),
+                ptr(distance_bias), dist_len, int(window or 0), float(scale), int(splits), ptr(workspace), *extras, int(row_hi), ptr(status), stream()),
             "attention_general (tensor cores)",
         )
         if splits > 1:
@@ -714,7 +829,7 @@ def attention_general(
             ptr(q), int(q_strides[0]), int(q_strides[1]), ptr(k_cache), k_row, int(k_dim), ptr(v_cache), v_row,
             int(v_dim), ptr(out), int(o_strides[0]), int(o_strides[1]), code(q), ptr(block_table),
             block_table.shape[1], page_size, num_pages, nkv, int(num_q_heads), ptr(positions), ptr(token_entry),
-            ptr(slopes), int(window or 0), float(scale), *extras, n, ptr(status), stream(),
+            ptr(slopes), ptr(distance_bias), dist_len, int(window or 0), float(scale), *extras, n, ptr(status), stream(),
         ),
         "attention_general",
     )

@@ -1,6 +1,6 @@
 """Parts of a layer: norms, position encodings, mixers, feed-forwards, blocks."""
 
-from . import attention, block, ffn, latent_attention, linear_recurrence, moe, norms, positions  # noqa: F401  (registers the kinds)
+from . import attention, block, ffn, gated_recurrence, latent_attention, linear_recurrence, moe, norms, positions  # noqa: F401  (registers the kinds)
 from .base import (
     BuildContext,
     CacheView,

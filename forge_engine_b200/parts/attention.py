@@ -10,6 +10,7 @@ head_dim, window) between steps.
 from __future__ import annotations
 
 import functools
+import math
 import os
 
 import torch
@@ -136,6 +137,7 @@ class GQAttention(Mixer):
         return (getattr(spec, "v_head_dim", None) not in (None, spec.head_dim)
                 or (spec.qk_norm and getattr(spec, "qk_norm_scope", "head") == "whole")
                 or getattr(spec, "distance_bias_base", None) is not None
+                or getattr(spec, "distance_bias_table", None) is not None or not getattr(spec, "kv_projection", True)
                 or bool(getattr(spec, "keep_first", 0)) or getattr(spec, "softcap", None) is not None
                 or getattr(spec, "query_temperature", None) is not None or bool(getattr(spec, "head_gate", False))
                 or getattr(spec, "differential", None) is not None)
@@ -167,6 +169,12 @@ class GQAttention(Mixer):
         bias = None
         rows = [self.nq * self.parts * self.d, self.nkv * self.parts * self.d, self.nkv * self.dv]
         names = [name("q_proj.weight"), name("k_proj.weight"), name("v_proj.weight")]
+        # a layer without keys and values of its own projects queries only and reads another run's cache
+        self.kv_projection = bool(getattr(spec, "kv_projection", True))
+        if not self.kv_projection:
+            if spec.bias or self.head_gate:
+                raise ConfigError("a layer without key and value projections takes no biases and no gates")
+            rows, names = rows[:1], names[:1]
         if self.head_gate:
             # the gates' logits are further columns of the same product
             rows.append(self.nq)
@@ -194,10 +202,34 @@ class GQAttention(Mixer):
         if base is not None:
             heads = torch.arange(1, self.nq + 1, dtype=torch.float64)
             self.slopes = (float(base) ** (-heads / self.nq)).float().to(ctx.device).contiguous()
+        self.distance_bias = None
+        table = getattr(spec, "distance_bias_table", None)
+        if table is not None:
+            self.distance_bias = self.expand_distance_bias(weights[name("rel")], float(table[1])).to(ctx.device)
         self._slots = None
         self.plan_key = ("gqa_attention", self.nq, self.nkv, self.d, spec.window) + (
             ("general", self.dv, self.parts, self.keep_first) if self.general else ())
         self.last_splits = None   # what the last step's decode entries ran with (0: balanced kernel)
+
+    @staticmethod
+    def expand_distance_bias(stored: torch.Tensor, far: float) -> torch.Tensor:
+        """The learned bias by distance, one entry per distance: 32-bit [heads, L].  ``stored``
+        [rows, heads]: distance n reads row n below h = rows // 2, and beyond that row
+        min(rows - 1, h + floor(ln(n / h) / ln(far / h) * (rows - h))), which widens
+        logarithmically and reaches the last row at distance ``far``; the kernels clamp the
+        distance to L - 1, the first one that reads the last row."""
+        rows = int(stored.shape[0])
+        half = rows // 2
+        if half < 1 or far <= half:
+            raise ConfigError(f"a distance bias of {rows} rows needs at least 2 rows and its far distance ({far}) above {half}")
+        reach = int(math.ceil(far)) + 1
+        if reach > (1 << 22):
+            raise UnsupportedShapeError(f"a distance bias that widens up to distance {far} is not implemented")
+        n = torch.arange(reach, dtype=torch.float64)
+        wide = half + torch.floor(torch.log(n.clamp(min=1) / half) / math.log(far / half) * (rows - half))
+        bucket = torch.where(n < half, n, wide.clamp(max=rows - 1)).long()
+        last = int((bucket == rows - 1).nonzero()[0]) if bool((bucket == rows - 1).any()) else reach - 1
+        return stored.detach().float().cpu()[bucket[: last + 1]].t().contiguous()
 
     @classmethod
     def weight_shapes(cls, spec) -> dict:
@@ -211,6 +243,11 @@ class GQAttention(Mixer):
             name("v_proj.weight"): WeightInfo((spec.num_kv_heads * dv, h)),
             name("o_proj.weight"): WeightInfo((h, spec.num_heads * dv)),
         }
+        if not getattr(spec, "kv_projection", True):
+            del shapes[name("k_proj.weight")], shapes[name("v_proj.weight")]
+        if getattr(spec, "distance_bias_table", None) is not None:
+            # rows None: the stored tensor says how many rows the table has
+            shapes[name("rel")] = WeightInfo((spec.distance_bias_table[0], spec.num_heads), "bias")
         if getattr(spec, "head_gate", False):
             shapes[name("gate_proj.weight")] = WeightInfo((spec.num_heads, h))
         if parts > 1:
@@ -299,6 +336,8 @@ class GQAttention(Mixer):
                 mode = native.PREP_NORM_WHOLE if self.spec.qk_norm_scope == "whole" else native.PREP_NORM_HEAD
             q = torch.empty((n, nq * d), dtype=k_cache.dtype, device=x.device)
             q_end, k_end = nq * d, (nq + nkv) * d
+            if not self.kv_projection and cache.owns:
+                raise ConfigError("a layer without key and value projections must read another run's cache")
             native.qkv_prepare(
                 q=qkv[:, :q_end], q_heads=nq, q_dim=d, q_norm=(mode, d, self.q_norm), q_out=q, q_out_strides=(nq * d, d),
                 k=qkv[:, q_end:k_end] if cache.owns else None, k_heads=nkv, k_dim=d, k_norm=(mode, d, self.k_norm),
@@ -328,7 +367,8 @@ class GQAttention(Mixer):
                                          splits=splits, keep_first=self.keep_first,
                                          softcap=self.softcap, query_temperature=self.query_temperature, parts=parts,
                                          part_strides=(self.d, self.d, dv) if parts > 1 else (0, 0, 0),
-                                         gate=gate, row_hi=SHORT_ENTRY_ROWS if long_entries else 0)
+                                         gate=gate, row_hi=SHORT_ENTRY_ROWS if long_entries else 0,
+                                         distance_bias=self.distance_bias)
             if parts > 1:
                 maps = out
                 out = torch.empty((n, nq * dv), dtype=k_cache.dtype, device=x.device)
@@ -389,7 +429,7 @@ class GQAttention(Mixer):
         """Whether prompt portions of this (general) layer run on the tcgen05 prefill kernel:
         a plain softmax over one map per head (a window, kept first tokens and a gate per head
         it has), keys and values of 64 or 128."""
-        return (self.parts == 1 and self.slopes is None and self.softcap is None and self.query_temperature is None
+        return (self.parts == 1 and self.slopes is None and self.distance_bias is None and self.softcap is None and self.query_temperature is None
                 and self.spec.scale > 0 and native.prefill_tc5_takes(self.ctx.dtype, self.d, self.dv, self.nq // self.nkv, page_size)
                 and native.general_mma_takes(self.ctx.dtype, self.d, self.dv))
 

@@ -52,7 +52,7 @@ class WeightInfo:
     """Shape and role of one tensor; the role picks the random initialiser."""
 
     shape: tuple
-    # "matrix" N(0, std) | "norm" 1 + N(0, 0.1) | "bias" N(0, std) | "identity" I + N(0, 0.1)
+    # "matrix" N(0, std) | "norm" 1 + N(0, 0.1) | "bias" N(0, std) | "identity" I + N(0, 0.1) | "small" N(0, 0.1)
     role: str = "matrix"
 
 
@@ -63,13 +63,16 @@ class CacheView:
     ``kv`` is ``(k_cache, v_cache)`` [pages, kv_heads, page_size, head_dim] or None;
     ``group`` indexes ``StepBatch.group_tables``; ``owns`` is False when the run reads
     another run's cache and must not write; ``state`` is [max_requests + 1, *shape] or None
-    and is indexed by ``StepBatch.slots`` (the last row belongs to filler entries).
+    and is indexed by ``StepBatch.slots`` (the last row belongs to filler entries);
+    ``own_state`` likewise, for what the run declared as ``CacheNeeds.own_state`` (its own
+    also where ``owns`` is False).
     """
 
     kv: tuple | None
     group: int | None
     owns: bool
     state: object = None
+    own_state: object = None
 
 
 class Part:

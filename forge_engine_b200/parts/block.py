@@ -219,3 +219,123 @@ class StreamMixBlock:
 
 register_arrangement("pre_norm", PreNormBlock, replace=True)
 register_arrangement("stream_mix", StreamMixBlock, replace=True)
+
+
+class SandwichConvBlock:
+    """Sublayers with a norm on both sides and a short causal convolution on their input.
+
+    x += norm_b(sublayer(u)) with u = y + conv(y), y = norm(x): for the mixer, then for the
+    feed-forward if the layer has one.  The residual stream ``h`` is 32-bit.  A sublayer's
+    update is handed on unadded, with the norm that still has to be taken of it, and one kernel
+    launch normalises it, adds it and normalises the stream for the next sublayer; the
+    convolution runs on those 32-bit rows and rounds once, for the sublayer's projections.
+    The last taps - 1 rows of y of either sublayer are the block's own state per request
+    (``CacheNeeds.own_state`` [2, taps - 1, hidden]), its own also in a layer that reads
+    another layer's keys and values."""
+
+    roles = ("input_norm", "mixer", "mixer_out_norm", "post_norm", "ffn", "ffn_out_norm", "conv")
+
+    def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
+        from ..config.specs import local_name
+
+        self.ctx = ctx
+        options = spec.options
+        self.taps = int(options.taps)
+        if not 1 <= self.taps <= native.CONV_MAX_TAPS:
+            raise ValueError(f"a convolution of {self.taps} taps; the kernel takes 1 to {native.CONV_MAX_TAPS}")
+        self.width = spec.input_norm.size
+        self.input_norm = build_part(spec.input_norm, weights["input_norm"], ctx)
+        self.mixer = build_part(spec.mixer, weights["mixer"], ctx)
+        self.mixer_out_norm = build_part(options.mixer_out_norm, weights["mixer_out_norm"], ctx)
+        self.post_norm = self.ffn = self.ffn_out_norm = None
+        if spec.ffn is not None:
+            self.post_norm = build_part(spec.post_norm, weights["post_norm"], ctx)
+            self.ffn = build_part(spec.ffn, weights["ffn"], ctx)
+            self.ffn_out_norm = build_part(options.ffn_out_norm, weights["ffn_out_norm"], ctx)
+        # stored [hidden, taps]; the kernel reads a tap's weights side by side
+        self.conv = [weights["conv"][local_name(options, key)].to(device=ctx.device, dtype=torch.float32).t().contiguous()
+                     for key in (("conv1", "conv2") if spec.ffn is not None else ("conv1",))]
+
+    @classmethod
+    def weight_shapes(cls, spec) -> dict:
+        """role -> {local name -> WeightInfo}"""
+        from ..config.specs import local_name
+
+        options = spec.options
+        shape = WeightInfo((spec.input_norm.size, options.taps), "small")
+        shapes = {"input_norm": part_class(spec.input_norm).weight_shapes(spec.input_norm),
+                  "mixer": part_class(spec.mixer).weight_shapes(spec.mixer),
+                  "mixer_out_norm": part_class(options.mixer_out_norm).weight_shapes(options.mixer_out_norm),
+                  "conv": {local_name(options, "conv1"): shape}}
+        if spec.ffn is not None:
+            shapes["post_norm"] = part_class(spec.post_norm).weight_shapes(spec.post_norm)
+            shapes["ffn"] = part_class(spec.ffn).weight_shapes(spec.ffn)
+            shapes["ffn_out_norm"] = part_class(options.ffn_out_norm).weight_shapes(options.ffn_out_norm)
+            shapes["conv"][local_name(options, "conv2")] = shape
+        return shapes
+
+    def cache_needs(self):
+        import dataclasses
+
+        from ..cache.manager import StateSpec
+
+        needs = self.mixer.cache_needs()
+        if self.taps > 1:
+            needs = dataclasses.replace(needs, own_state=StateSpec((2, self.taps - 1, self.width), "float32"))
+        return needs
+
+    def plan_step(self, entries: list, page_size: int, plans: dict) -> None:
+        planner = getattr(self.mixer, "plan_step", None)
+        if planner is not None:
+            planner(entries, page_size, plans)
+
+    @property
+    def graph_safe(self) -> bool:
+        parts = [self.input_norm, self.mixer, self.mixer_out_norm]
+        if self.ffn is not None:
+            parts += [self.post_norm, self.ffn, self.ffn_out_norm]
+        return all(getattr(part, "graph_safe", False) for part in parts)
+
+    def _enter(self, h, pending, norm, sublayer: int, batch, cache: CacheView):
+        """Add what is pending (normalised), normalise the stream, convolve: the sublayer's input."""
+        update = out_norm = None
+        if isinstance(pending, tuple):
+            update, out_norm = pending
+        elif pending is not None:
+            h.add_(pending)              # a block of another arrangement handed a plain update on
+        y = torch.empty(h.shape, dtype=torch.float32, device=h.device)
+        native.add_normed_rmsnorm(h, update, None if out_norm is None else out_norm.weight, norm.weight, y,
+                                  0.0 if out_norm is None else out_norm.eps, norm.eps)
+        u = torch.empty(h.shape, dtype=self.ctx.dtype, device=h.device)
+        state = None if cache.own_state is None else cache.own_state[:, sublayer]
+        native.causal_conv_state(y, self.conv[sublayer], state, batch.slots, batch.cu_tokens, batch.token_entry, u,
+                                 batch.n_entries)
+        return u
+
+    def forward(self, h, pending, batch, cache: CacheView):
+        with self.ctx.section("input_norm"):
+            u = self._enter(h, pending, self.input_norm, 0, batch, cache)
+        with self.ctx.section("mixer"):
+            update = self.mixer.forward(u, batch, cache)
+        pending = (update, self.mixer_out_norm)
+        if self.ffn is None:
+            return pending
+        with self.ctx.section("post_norm"):
+            u = self._enter(h, pending, self.post_norm, 1, batch, cache)
+        with self.ctx.section("ffn"):
+            update = self.ffn.forward(u)
+        return (update, self.ffn_out_norm)
+
+    def close(self, h, pending, final_norm, row_map):
+        """The model's last step: the pending update is normalised and added and the final norm
+        taken, for the rows of ``row_map`` only and without writing the stream."""
+        update, out_norm = pending if isinstance(pending, tuple) else (pending, None)
+        normed = torch.empty((row_map.numel(), h.shape[-1]), dtype=self.ctx.dtype, device=h.device)
+        if out_norm is None:
+            return final_norm.add_forward(h, update, row_map=row_map)
+        native.add_normed_rmsnorm(h, update, out_norm.weight, final_norm.weight, normed, out_norm.eps, final_norm.eps,
+                                  row_map=row_map, write_residual=False)
+        return normed
+
+
+register_arrangement("sandwich_conv", SandwichConvBlock, replace=True)

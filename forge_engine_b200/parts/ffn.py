@@ -72,4 +72,47 @@ class GatedMLP(FeedForward):
         return self.down(act)
 
 
+class DenseMLP(FeedForward):
+    """down(act(up(x) + b_up)) + b_down without a gate.  The activation is taken of the
+    projection's 32-bit sums plus the bias, in 32-bit, and rounded once.
+
+    "xielu": act(z) = a_pos z^2 + z / 2 for z > 0 and a_neg (exp(z) - 1 - z) + z / 2 otherwise,
+    with a_pos = softplus(p) and a_neg = 1/2 + softplus(q) from the two learned numbers
+    ``act`` = (p, q), worked out once when the layer is built."""
+
+    graph_safe = True
+
+    def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
+        if spec.activation != "xielu":
+            raise ConfigError(f"activation {spec.activation!r} is not implemented; known: xielu")
+        self.ctx = ctx
+        self.inter = spec.intermediate_size
+        name = lambda canonical: local_name(spec, canonical)  # noqa: E731
+        self.up = Linear(weights[name("up_proj.weight")], status=ctx.status)
+        self.up_bias = weights[name("up_proj.bias")].to(device=ctx.device, dtype=torch.float32).contiguous() if spec.bias else None
+        self.down = Linear(weights[name("down_proj.weight")], weights[name("down_proj.bias")] if spec.bias else None,
+                           status=ctx.status)
+        p, q = (float(v) for v in weights[name("act")].double().cpu())
+        softplus = lambda z: float(torch.nn.functional.softplus(torch.tensor(z, dtype=torch.float64), threshold=1e9))  # noqa: E731
+        self.a_pos, self.a_neg = softplus(p), 0.5 + softplus(q)
+
+    @classmethod
+    def weight_shapes(cls, spec) -> dict:
+        h, i = spec.hidden_size, spec.intermediate_size
+        name = lambda canonical: local_name(spec, canonical)  # noqa: E731
+        shapes = {name("up_proj.weight"): WeightInfo((i, h)), name("down_proj.weight"): WeightInfo((h, i)),
+                  name("act"): WeightInfo((2,), "small")}
+        if spec.bias:
+            shapes[name("up_proj.bias")] = WeightInfo((i,), "bias")
+            shapes[name("down_proj.bias")] = WeightInfo((h,), "bias")
+        return shapes
+
+    def forward(self, x):
+        sums = self.up(x, out_dtype=torch.float32)
+        act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
+        native.bias_xielu(sums, self.up_bias, act, self.a_pos, self.a_neg)
+        return self.down(act, out_dtype=torch.float32)
+
+
 register_part("gated_mlp", GatedMLP, replace=True)
+register_part("dense_mlp", DenseMLP, replace=True)

@@ -41,8 +41,11 @@ class RoutedMLP(FeedForward):
             raise ConfigError(f"router score {spec.score!r}; known: sigmoid, softmax")
         if spec.weight_on not in ("input", "output"):
             raise ConfigError(f"weight_on={spec.weight_on!r}; known: input, output")
-        if not 1 <= spec.top <= min(spec.experts, MAX_TOP):
-            raise ConfigError(f"top={spec.top} of {spec.experts} experts; at most {MAX_TOP}")
+        self.identity = int(getattr(spec, "identity", 0) or 0)
+        if not 1 <= spec.top <= min(spec.experts + self.identity, MAX_TOP):
+            raise ConfigError(f"top={spec.top} of {spec.experts + self.identity} experts; at most {MAX_TOP}")
+        if self.identity and spec.weight_on != "output":
+            raise ConfigError("identity experts take the weight on the output")
         unit = spec.expert
         if unit.activation not in ACTIVATIONS:
             raise ConfigError(f"activation {unit.activation!r} is not implemented")
@@ -52,7 +55,13 @@ class RoutedMLP(FeedForward):
         self.weight_on_input = spec.weight_on == "input"
         self.activation = ACTIVATIONS[unit.activation]
         self.limit, self.slope = float(unit.limit or 0.0), float(unit.slope)
-        # the router's rows, and under them the shared unit's gate row: one 32-bit product
+        self.groups = getattr(spec, "groups", None)
+        self.renorm_floor = float(getattr(spec, "renorm_floor", 0.0))
+        self.weight_scale = float(getattr(spec, "weight_scale", 1.0))
+        self.correction = None
+        if getattr(spec, "correction", False):
+            self.correction = weights["correction"].to(device=ctx.device, dtype=torch.float32).contiguous()
+        # the router's rows (identity units' last), and under them the shared unit's gate row: one 32-bit product
         rows = [weights["router"]]
         self.shared = None
         self.shared_gate = False
@@ -92,12 +101,15 @@ class RoutedMLP(FeedForward):
             self.shared = build_part(_shared_spec(spec), weights, ctx)
         # rows per expert, counted by the route kernel; the plan kernel reads them and leaves
         # zeros behind, so no launch is spent on clearing them
-        self.counts = torch.zeros(self.experts, dtype=torch.int32, device=ctx.device)
+        self.counts = torch.zeros(self.experts + 1, dtype=torch.int32, device=ctx.device)
 
     @classmethod
     def weight_shapes(cls, spec) -> dict:
         h, unit = spec.hidden_size, spec.expert
-        shapes = {"router": WeightInfo((spec.experts, h))}
+        outputs = spec.experts + int(getattr(spec, "identity", 0) or 0)
+        shapes = {"router": WeightInfo((outputs, h))}
+        if getattr(spec, "correction", False):
+            shapes["correction"] = WeightInfo((outputs,), "bias")
         names = [local_name(unit, n) for n in ("gate_proj.weight", "up_proj.weight", "down_proj.weight")]
         for e in range(spec.experts):
             shapes[f"e{e}.{names[0]}"] = WeightInfo((unit.intermediate_size, h))
@@ -133,10 +145,11 @@ class RoutedMLP(FeedForward):
         tile_rows = self.tile_rows(slots) if self.fused else 0
         max_tiles = native.moe_max_tiles(slots, self.experts, tile_rows)
         with section("ffn.route"):
-            ints = torch.empty(4 * slots + self.experts + 1 + 2 * max_tiles, dtype=torch.int32, device=device)
+            ints = torch.empty(4 * slots + self.experts + 2 + 2 * max_tiles, dtype=torch.int32, device=device)
             weight = torch.empty(slots, dtype=torch.float32, device=device)
             plan = native.moe_route(logits, self.experts, self.top, self.softmax, self.renormalise, self.counts, ints,
-                                    weight, max_tiles, tile_rows)
+                                    weight, max_tiles, tile_rows, identity=self.identity, correction=self.correction,
+                                    groups=self.groups, renorm_floor=self.renorm_floor, weight_scale=self.weight_scale)
         hidden = torch.empty((slots, self.inter), dtype=x.dtype, device=device)
         rows = torch.empty((slots, self.width), dtype=torch.float32, device=device)
         with section("ffn.experts"):
@@ -157,7 +170,9 @@ class RoutedMLP(FeedForward):
         with section("ffn.combine"):
             out = torch.empty((n, self.width), dtype=torch.float32, device=device)
             native.moe_combine(rows, plan, self.top, out, slot_weight=None if self.weight_on_input else weight,
-                               shared=shared, shared_logit=logits[:, self.experts] if self.shared_gate else None)
+                               shared=shared,
+                               shared_logit=logits[:, self.experts + self.identity] if self.shared_gate else None,
+                               identity_input=x if self.identity else None, experts=self.experts)
         return out
 
 

@@ -19,11 +19,16 @@ class RMSNorm(Norm):
         self.size = spec.size
         self.eps = float(spec.eps)
         self.weight = weights[local_name(spec, "weight")].to(device=ctx.device, dtype=torch.float32).contiguous()
+        offset = float(getattr(spec, "weight_offset", 0.0) or 0.0)
+        if offset:
+            # the stored weight is the distance from ``offset``; the sum is taken once, in 32-bit
+            self.weight = (self.weight + offset).contiguous()
         self.dtype = ctx.dtype
 
     @classmethod
     def weight_shapes(cls, spec) -> dict:
-        return {local_name(spec, "weight"): WeightInfo((spec.size,), "norm")}
+        stored_near_zero = bool(getattr(spec, "weight_offset", 0.0))
+        return {local_name(spec, "weight"): WeightInfo((spec.size,), "small" if stored_near_zero else "norm")}
 
     def add_forward(self, residual, update, row_map=None, shift=None):
         """residual (32-bit [N, size]) += update (+ ``shift``, a 32-bit vector added to every

@@ -183,7 +183,9 @@ def open_checkpoint(
                     missing.append(name)
                     continue
                 shape = tuple(handle.get_slice(name).get_shape())
-                if shape != tuple(expected[name].shape):
+                wanted = tuple(expected[name].shape)
+                # an extent the model leaves open (None) is whatever the file holds
+                if len(shape) != len(wanted) or any(w is not None and w != g for w, g in zip(wanted, shape)):
                     wrong.append(f"{name}: stored {shape}, model needs {tuple(expected[name].shape)}")
                 stored = _stored_dtype(handle, name)
                 if getattr(expected[name], "role", "matrix") in ("matrix", "norm", "bias", "identity") and stored not in _FLOAT_NAMES:

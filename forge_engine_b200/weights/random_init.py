@@ -42,6 +42,9 @@ class RandomTensors(Mapping):
 
     def __getitem__(self, name: str) -> torch.Tensor:
         info = self._expected[name]
+        if any(extent is None for extent in info.shape):
+            raise ValueError(f"{name}: the model leaves an extent open that only a stored tensor says; "
+                             "random weights need it in the configuration")
         generator = torch.Generator(device=self.device).manual_seed(self.seed * 1_000_003 + self._index[name])
         out = torch.empty(info.shape, dtype=self.dtype, device=self.device)
         flat = out.view(-1)
@@ -51,7 +54,7 @@ class RandomTensors(Mapping):
             count = min(self.PIECE, flat.numel() - begin)
             noise = torch.randn(count, generator=generator, dtype=torch.float32, device=self.device)
             flat[begin : begin + count] = (noise.mul_(0.1).add_(1.0) if info.role == "norm"
-                                           else noise.mul_(0.1) if info.role == "identity" else noise.mul_(self.std))
+                                           else noise.mul_(0.1) if info.role in ("identity", "small") else noise.mul_(self.std))
             del noise
         if info.role == "identity":
             out.add_(torch.eye(info.shape[0], info.shape[1], dtype=self.dtype, device=self.device))
