@@ -536,8 +536,8 @@ DESIGN_SIZES = {
 def design_compare(args) -> int:
     """Prefill (one 2,048-token prompt) and decode (batch 8, 2,048-token contexts) of models
     of `--layers` (4) layers of one kind: the Qwen3 layer, the Zofadra attention, latent
-    attention and linear-recurrence layers and the Tekilorn differential, gated window and
-    routed layers at the same sizes, plus a model of each design that mixes its layers.
+    attention and linear-recurrence layers, the Tekilorn differential, gated window and
+    routed layers and the Zabutar gated-recurrence, biased-attention and routed layers at the same sizes, plus a model of each design that mixes its layers.
     One JSON line per model: tokens/s, ms per step, the median device time of every part of a
     step (CUDA events round each part, in a second runner) and, for the token-mixing kernel,
     its share of the measured peaks (prefill: its flops over the library GEMM's burst rate;
@@ -609,6 +609,29 @@ def design_compare(args) -> int:
             "tekilorn-mixed": tekilorn([differential, dict(gated, mlp=routed), dict(gated, mlp=routed), gated],
                                        loop={"start": 1, "stop": 3, "times": 2}),
         })
+        # Zabutar at the same sizes: the gated recurrence with the state sizes of the Zofadra
+        # recurrence, attention with the learned bias by distance at Qwen3's head sizes, the dense
+        # xIELU feed-forward of ff, and a routed one with as many active weights per token as the
+        # dense one (2 of 16 experts of ff / 4 and 2 identity units in 3 groups of which 2 are
+        # kept, a shared unit of ff / 2)
+        z_dense = {"kind": "dense", "ff": z["ff"]}
+        z_routed = {"kind": "moe", "expert": {"ff": z["ff"] // 4}, "shared": {"ff": z["ff"] // 2},
+                    "router": {"experts": 16, "identity": 2, "top": 2, "scale": 2.5, "groups": {"count": 3, "keep": 2}}}
+        z_recurrence = {"type": "hgrn2", "mlp": z_dense, "mixer": {"heads": H, "dim": rec["dim"], "vdim": rec["vdim"]}}
+        z_attention = {"type": "attention", "mlp": z_dense, "mixer": {
+            "heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "bias_max": 1024, "bias_rows": 32}}
+
+        def zabutar(kinds):
+            return {"architecture": "Zabutar", "vocab": vocab, "width": W, "norm": {"eps": 1e-5}, "canon": {"taps": 4},
+                    "max_positions": CONTEXT + 128, "layers": kinds}
+
+        models.update({
+            "zabutar-recurrence": zabutar([z_recurrence] * layers),
+            "zabutar-attention": zabutar([z_attention] * layers),
+            "zabutar-routed": zabutar([dict(z_recurrence, mlp=z_routed)] * layers),
+            "zabutar-mixed": zabutar([z_recurrence, dict(z_recurrence, mlp=z_routed), z_attention,
+                                      dict(z_attention, mixer=dict(z_attention["mixer"], kv_from=2), mlp=z_routed)]),
+        })
         if args.design_models:
             wanted = [w for w in args.design_models.split(",") if w]
             models = {name: raw for name, raw in models.items() if any(name.startswith(w) for w in wanted)}
@@ -626,10 +649,13 @@ def design_compare(args) -> int:
                                 batch * (window + keep) * G * 2 * D * 2),
         }
         mixer_cost["tekilorn-routed"] = mixer_cost["tekilorn-window"]
+        mixer_cost["zabutar-recurrence"] = mixer_cost["zabutar-routed"] = mixer_cost["zofadra-recurrence"]
+        mixer_cost["zabutar-attention"] = mixer_cost["qwen3"]
         mixer_part = {"qwen3": "mixer.attention", "qwen3-window": "mixer.attention", "zofadra-attention": "mixer.attention",
                       "zofadra-latent": "mixer.attention", "zofadra-recurrence": "mixer.recurrence",
                       "tekilorn-differential": "mixer.attention", "tekilorn-window": "mixer.attention",
-                      "tekilorn-routed": "mixer.attention"}
+                      "tekilorn-routed": "mixer.attention", "zabutar-recurrence": "mixer.recurrence",
+                      "zabutar-routed": "mixer.recurrence", "zabutar-attention": "mixer.attention"}
         for name, raw in models.items():
             n_layers = len(raw["layers"]) if "layers" in raw else raw["num_hidden_layers"]
             pages = batch * (-(-(CONTEXT + 64) // PAGE) + 1) + -(-CONTEXT // PAGE) + 8
@@ -742,7 +768,7 @@ def main() -> int:
                         help="only the mixed step: 8 requests decoding beside a prompt portion, TOKENS tokens in all "
                              "(with --kernel-times: the kernels of one such step)")
     parser.add_argument("--design-compare", metavar="WIDTH", choices=sorted(DESIGN_SIZES) + ["all"],
-                        help="prefill and decode of the Zofadra and Tekilorn layer kinds beside the Qwen3 layer at equal size")
+                        help="prefill and decode of the Zofadra, Tekilorn and Zabutar layer kinds beside the Qwen3 layer at equal size")
     parser.add_argument("--design-models", metavar="NAMES", default="",
                         help="with --design-compare: only the models whose names start with one of these (comma-separated), "
                              "e.g. qwen3,tekilorn")
