@@ -73,6 +73,10 @@ struct AttnParams {
   int keep_first = 0;
   const float* gate = nullptr;
   long long gate_stride = 0;
+  // dist_bias[head * dist_len + min(query position - key position, dist_len - 1)] is added to
+  // the score before it is scaled, so the table holds the bias divided by the scale.
+  const float* dist_bias = nullptr;
+  int dist_len = 0;
 };
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) {
@@ -1081,7 +1085,7 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
       if (mk && mv && make_query_map(&mq, q, q_stride, total_tokens, num_kv_heads * groups, groups) == 0) {
         static bool tc5_configured = false;
         if (!tc5_configured) {
-          const cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+          const cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                      (int)TC5_SMEM);
           if (e != cudaSuccess) return (int)e;
           tc5_configured = true;
@@ -1089,7 +1093,7 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
         const int query_blocks = (max_rows + TC5_BLOCK_ROWS - 1) / TC5_BLOCK_ROWS;
         if (query_blocks > 65535) return FE_ERR_TOO_LARGE;
         dim3 grid(num_kv_heads, entries, query_blocks);
-        const int rc = fe_launch_dependent(attn_prefill_tc5_kernel, grid, dim3(TC5_THREADS), TC5_SMEM, stream, mq, *mk,
+        const int rc = fe_launch_dependent(attn_prefill_tc5_kernel<false>, grid, dim3(TC5_THREADS), TC5_SMEM, stream, mq, *mk,
                                            *mv, p);
         if (rc) return rc;
       } else {
@@ -1180,8 +1184,10 @@ FE_EXPORT int SYM(fe_attention_prefill_tc5_d)(const void* q, int q_stride, void*
                                               int num_pages, int num_kv_heads, int groups, const int* cu_tokens,
                                               const int* starts, int entries, int max_new, int total_tokens, int window,
                                               int keep_first, float scale, const float* gate, long long gate_stride,
-                                              int row_lo, int* status, cudaStream_t stream) {
+                                              int row_lo, const float* dist_bias, int dist_len, int* status,
+                                              cudaStream_t stream) {
   if (entries <= 0 || max_new * groups <= row_lo) return 0;
+  if (dist_bias != nullptr && dist_len < 1) return FE_ERR_BAD_SHAPE;
   if (entries > 65535 || num_kv_heads > 65535) return FE_ERR_TOO_LARGE;
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return FE_ERR_BAD_ALIGN;
   if ((q_stride % 8) != 0) return FE_ERR_BAD_ALIGN;
@@ -1197,6 +1203,7 @@ FE_EXPORT int SYM(fe_attention_prefill_tc5_d)(const void* q, int q_stride, void*
   p.row_lo = row_lo; p.row_hi = 0x7fffffff;
   p.num_splits = 1; p.ws_acc = nullptr; p.ws_ml = nullptr; p.ws_count = nullptr; p.cluster_merge = 0;
   p.keep_first = keep_first; p.gate = gate; p.gate_stride = gate_stride;
+  p.dist_bias = dist_bias; p.dist_len = dist_len;
   CUtensorMap mk, mv, mq;
   if (!cache_map(&mk, k_cache, num_pages * num_kv_heads * page_size, page_size) ||
       !cache_map(&mv, v_cache, num_pages * num_kv_heads * page_size, page_size) ||
@@ -1204,14 +1211,18 @@ FE_EXPORT int SYM(fe_attention_prefill_tc5_d)(const void* q, int q_stride, void*
     return FE_ERR_BAD_SHAPE;
   static bool tc5_configured = false;
   if (!tc5_configured) {
-    const cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC5_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC5_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC5_SMEM);
     if (e != cudaSuccess) return (int)e;
     tc5_configured = true;
   }
   const int query_blocks = (max_new * groups + TC5_BLOCK_ROWS - 1) / TC5_BLOCK_ROWS;
   if (query_blocks > 65535) return FE_ERR_TOO_LARGE;
-  const int rc = fe_launch_dependent(attn_prefill_tc5_kernel, dim3(num_kv_heads, entries, query_blocks), dim3(TC5_THREADS),
-                                     TC5_SMEM, stream, mq, mk, mv, p);
+  const dim3 grid(num_kv_heads, entries, query_blocks);
+  const int rc = dist_bias != nullptr
+                     ? fe_launch_dependent(attn_prefill_tc5_kernel<true>, grid, dim3(TC5_THREADS), TC5_SMEM, stream, mq, mk, mv, p)
+                     : fe_launch_dependent(attn_prefill_tc5_kernel<false>, grid, dim3(TC5_THREADS), TC5_SMEM, stream, mq, mk, mv, p);
   return rc ? rc : fe_last_error();
 }
 

@@ -204,6 +204,7 @@ __device__ __forceinline__ Tc5Tile tc5_tile(int row0, int rows_total, int start,
   return t;
 }
 
+template <bool DIST_BIAS>     // with a learned bias by distance (AttnParams::dist_bias)
 __global__ void __launch_bounds__(TC5_THREADS, 1)
 attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, AttnParams p) {
@@ -424,6 +425,15 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
       for (int c = 0; c < TC5_KEYS / 32; ++c) tc5_ld32_issue(s_addr + c * 32, raw + c * 32);
       tc5_ld_wait();
+      if (DIST_BIAS && row_valid) {
+        // the learned bias of this row's head by distance (divided by the scale when the table was
+        // made, so that everything below stays as it is); keys ahead of the row are masked below
+        const float* bias_row = p.dist_bias + (size_t)(kvh * p.groups + row % p.groups) * p.dist_len;
+        const int far = p.dist_len - 1, d0 = pos - key0;
+#pragma unroll
+        for (int j = 0; j < TC5_KEYS; ++j)
+          raw[j] = __float_as_uint(__uint_as_float(raw[j]) + __ldg(bias_row + min(max(d0 - j, 0), far)));
+      }
       // every key of the tile visible to every row of the tile?
       const bool clear = key0 + TC5_KEYS - 1 <= mine.pos_first && key0 + TC5_KEYS <= mine.key_end &&
                          mine.row0 + TC5_ROWS <= rows_total && (p.window <= 0 || mine.pos_last - key0 < p.window);

@@ -18,12 +18,19 @@
 
 #define CONV_MAX_TAPS 8
 
-template <typename TU, typename TO>
+// V: elements a thread takes at a time (4 where the row's length is a multiple of 4; all rows
+// then start on 16 bytes).  The order of additions depends on V and the row's length alone.
+template <int V> __device__ __forceinline__ void sc_load(const float* p, float* v) { if constexpr (V == 4) load4(p, v); else v[0] = p[0]; }
+template <int V> __device__ __forceinline__ void sc_load(const bf16* p, float* v) { if constexpr (V == 4) load4(p, v); else v[0] = to_float(p[0]); }
+template <int V> __device__ __forceinline__ void sc_store(float* p, const float* v) { if constexpr (V == 4) store4(p, v); else p[0] = v[0]; }
+template <int V> __device__ __forceinline__ void sc_store(bf16* p, const float* v) { if constexpr (V == 4) store4(p, v); else p[0] = from_float<bf16>(v[0]); }
+
+template <typename TU, typename TO, int V>
 __global__ void __launch_bounds__(256)
 add_normed_rmsnorm_kernel(float* __restrict__ residual, const TU* __restrict__ update, const float* __restrict__ w_update,
                           const float* __restrict__ weight, TO* __restrict__ out, const int* __restrict__ row_map, int size,
                           float eps_update, float eps, int write_residual) {
-  extern __shared__ float row[];       // [size]
+  extern __shared__ __align__(16) float row[];       // [size]
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
@@ -34,28 +41,43 @@ add_normed_rmsnorm_kernel(float* __restrict__ residual, const TU* __restrict__ u
   if (update != nullptr) {
     const TU* upd = update + (size_t)src * size;
     float su = 0.f;
-    for (int i = threadIdx.x; i < size; i += blockDim.x) {
-      const float u = to_float(upd[i]);
-      row[i] = u;
-      su = fmaf(u, u, su);
+    for (int i = threadIdx.x * V; i < size; i += blockDim.x * V) {
+      float u[V];
+      sc_load<V>(upd + i, u);
+#pragma unroll
+      for (int k = 0; k < V; ++k) su = fmaf(u[k], u[k], su);
+      sc_store<V>(row + i, u);
     }
     const float inv_u = 1.f / sqrtf(block_sum(su, scratch) / (float)size + eps_update);
-    for (int i = threadIdx.x; i < size; i += blockDim.x) {
-      const float x = res[i] + row[i] * inv_u * w_update[i];
-      row[i] = x;
-      if (write_residual) res[i] = x;
-      ss = fmaf(x, x, ss);
+    for (int i = threadIdx.x * V; i < size; i += blockDim.x * V) {
+      float u[V], x[V], w[V];
+      sc_load<V>(row + i, u), sc_load<V>(res + i, x), sc_load<V>(w_update + i, w);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        x[k] = x[k] + u[k] * inv_u * w[k];
+        ss = fmaf(x[k], x[k], ss);
+      }
+      sc_store<V>(row + i, x);
+      if (write_residual) sc_store<V>(res + i, x);
     }
   } else {
-    for (int i = threadIdx.x; i < size; i += blockDim.x) {
-      const float x = res[i];
-      row[i] = x;
-      ss = fmaf(x, x, ss);
+    for (int i = threadIdx.x * V; i < size; i += blockDim.x * V) {
+      float x[V];
+      sc_load<V>(res + i, x);
+#pragma unroll
+      for (int k = 0; k < V; ++k) ss = fmaf(x[k], x[k], ss);
+      sc_store<V>(row + i, x);
     }
   }
   const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)size + eps);
   TO* dst = out + (size_t)r * size;
-  for (int i = threadIdx.x; i < size; i += blockDim.x) dst[i] = from_float<TO>(row[i] * inv * weight[i]);
+  for (int i = threadIdx.x * V; i < size; i += blockDim.x * V) {
+    float x[V], w[V];
+    sc_load<V>(row + i, x), sc_load<V>(weight + i, w);
+#pragma unroll
+    for (int k = 0; k < V; ++k) x[k] = x[k] * inv * w[k];
+    sc_store<V>(dst + i, x);
+  }
 }
 
 // residual 32-bit [*, size]; update [*, size] or null; w_update, weight 32-bit [size] (as they
@@ -68,15 +90,23 @@ FE_EXPORT int fe_add_normed_rmsnorm(float* residual, const void* update, int upd
   const size_t smem = (size_t)size * sizeof(float);
   if (smem > 200 * 1024) return FE_ERR_TOO_LARGE;
   int threads = 64;
-  while (threads < 256 && threads * 4 < size) threads <<= 1;
+  while (threads < 256 && threads * 8 < size) threads <<= 1;
   int rc = FE_ERR_BAD_DTYPE;
-#define LAUNCH(TU, TO)                                                                                                 \
+  const bool wide = size % 4 == 0 && (((uintptr_t)residual | (uintptr_t)update | (uintptr_t)w_update | (uintptr_t)weight |
+                                       (uintptr_t)out) & 15) == 0;
+#define LAUNCH_V(TU, TO, V)                                                                                            \
   do {                                                                                                                 \
     if (smem > 48 * 1024)                                                                                              \
-      cudaFuncSetAttribute(add_normed_rmsnorm_kernel<TU, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    rc = fe_launch_dependent(add_normed_rmsnorm_kernel<TU, TO>, dim3(rows), dim3(threads), smem, stream, residual,     \
+      cudaFuncSetAttribute(add_normed_rmsnorm_kernel<TU, TO, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                           (int)smem);                                                                                 \
+    rc = fe_launch_dependent(add_normed_rmsnorm_kernel<TU, TO, V>, dim3(rows), dim3(threads), smem, stream, residual,  \
                              (const TU*)update, w_update, weight, (TO*)out, row_map, size, eps_update, eps,            \
                              write_residual);                                                                          \
+  } while (0)
+#define LAUNCH(TU, TO)                                                                                                 \
+  do {                                                                                                                 \
+    if (wide) LAUNCH_V(TU, TO, 4);                                                                                     \
+    else LAUNCH_V(TU, TO, 1);                                                                                          \
   } while (0)
   if (update == nullptr) update_dtype = FE_DTYPE_F32;
   if (update_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32) LAUNCH(float, float);
@@ -84,13 +114,14 @@ FE_EXPORT int fe_add_normed_rmsnorm(float* residual, const void* update, int upd
   else if (update_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_F32) LAUNCH(bf16, float);
   else if (update_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_BF16) LAUNCH(bf16, bf16);
 #undef LAUNCH
+#undef LAUNCH_V
   return rc ? rc : fe_last_error();
 }
 
 // y 32-bit [tokens, width]; w 32-bit [taps, width] (tap j weighs the row taps - 1 - j tokens
 // back); state 32-bit, row `slot` at state + slot * state_stride holds [taps - 1, width], oldest
 // row first; out [tokens, width].
-template <typename TO>
+template <typename TO, int V>
 __global__ void __launch_bounds__(256)
 causal_conv_state_kernel(const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ state,
                          long long state_stride, const int* __restrict__ slots, const int* __restrict__ cu_tokens,
@@ -103,12 +134,23 @@ causal_conv_state_kernel(const float* __restrict__ y, const float* __restrict__ 
     const int t = blockIdx.x;
     const int first = cu_tokens[token_entry[t]];
     if (t - first < back) return;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-      float sum = 0.f;
+    for (int c = threadIdx.x * V; c < width; c += blockDim.x * V) {
+      float sum[V], own[V];
 #pragma unroll
-      for (int j = 0; j < CONV_MAX_TAPS; ++j)
-        if (j < taps) sum = fmaf(w[(size_t)j * width + c], y[(size_t)(t - back + j) * width + c], sum);
-      out[(size_t)t * width + c] = from_float<TO>(y[(size_t)t * width + c] + sum);
+      for (int k = 0; k < V; ++k) sum[k] = 0.f;
+#pragma unroll
+      for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+        if (j < taps) {
+          float wj[V];
+          sc_load<V>(w + (size_t)j * width + c, wj), sc_load<V>(y + (size_t)(t - back + j) * width + c, own);
+#pragma unroll
+          for (int k = 0; k < V; ++k) sum[k] = fmaf(wj[k], own[k], sum[k]);
+        }
+      }
+      // the last tap read the token's own row
+#pragma unroll
+      for (int k = 0; k < V; ++k) sum[k] = own[k] + sum[k];
+      sc_store<V>(out + (size_t)t * width + c, sum);
     }
     return;
   }
@@ -159,15 +201,16 @@ FE_EXPORT int fe_causal_conv_state(const float* y, const float* w, float* state,
   if (taps < 1 || taps > CONV_MAX_TAPS || width < 1) return FE_ERR_BAD_SHAPE;
   if (taps > 1 && state == nullptr) return FE_ERR_BAD_SHAPE;
   int threads = 64;
-  while (threads < 256 && threads < width) threads <<= 1;
+  while (threads < 256 && threads * 4 < width) threads <<= 1;
   const dim3 grid(n_tokens + (taps > 1 ? n_entries : 0));
+  const bool wide = width % 4 == 0 && (((uintptr_t)y | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
   int rc;
-  if (out_dtype == FE_DTYPE_F32)
-    rc = fe_launch_dependent(causal_conv_state_kernel<float>, grid, dim3(threads), 0, stream, y, w, state, state_stride,
-                             slots, cu_tokens, token_entry, (float*)out, n_tokens, width, taps);
-  else if (out_dtype == FE_DTYPE_BF16)
-    rc = fe_launch_dependent(causal_conv_state_kernel<bf16>, grid, dim3(threads), 0, stream, y, w, state, state_stride,
-                             slots, cu_tokens, token_entry, (bf16*)out, n_tokens, width, taps);
+#define LAUNCH(TO, V)                                                                                                  \
+  rc = fe_launch_dependent(causal_conv_state_kernel<TO, V>, grid, dim3(threads), 0, stream, y, w, state, state_stride, \
+                           slots, cu_tokens, token_entry, (TO*)out, n_tokens, width, taps)
+  if (out_dtype == FE_DTYPE_F32) { if (wide) LAUNCH(float, 4); else LAUNCH(float, 1); }
+  else if (out_dtype == FE_DTYPE_BF16) { if (wide) LAUNCH(bf16, 4); else LAUNCH(bf16, 1); }
   else return FE_ERR_BAD_DTYPE;
+#undef LAUNCH
   return rc ? rc : fe_last_error();
 }

@@ -66,7 +66,9 @@ def _declare(handle: ctypes.CDLL) -> None:
                                  i, f, f, i, i, ll, i, ll, p, ll, i, i, p, p],
         "fe_differential_combine": [p, p, i, ll, i, f, f, f, p],
         "fe_bias_xielu": [p, i, p, p, i, ll, i, f, f, p],
-        "fe_gated_recurrence": [p, ll, i, i, i, p, p, p, f, p, i, p, p, p, i, i, i, i, i, p, p],
+        "fe_gated_recurrence": [p, ll, i, i, i, p, p, p, f, p, i, p, p, p, i, i, i, i, i, i, i, p, p, p],
+        "fe_gated_recurrence_scratch": [i, i, i, i, i],
+        "fe_gated_recurrence_long_from": [],
         "fe_add_normed_rmsnorm": [p, p, i, p, p, p, i, p, i, i, f, f, i, p],
         "fe_causal_conv_state": [p, p, p, ll, p, p, p, p, i, i, i, i, i, p],
         "fe_moe_route": [p, ll, i, i, i, i, i, p, p, p, p, p, p, p, p, p, i, i, i, p, i, i, f, f, p],
@@ -95,6 +97,7 @@ def _declare(handle: ctypes.CDLL) -> None:
         fn = getattr(handle, name)
         fn.argtypes = argtypes
         fn.restype = c_int
+    handle.fe_gated_recurrence_scratch.restype = ctypes.c_longlong
     handle.fe_uniform_host.argtypes = [c_ulonglong, c_ulonglong]
     handle.fe_uniform_host.restype = c_float
 
@@ -137,11 +140,14 @@ def prefill_tc5_takes(dtype, head_dim: int, value_dim: int, groups: int, page_si
 def attention_prefill_tc5(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                           block_table: torch.Tensor, cu_tokens: torch.Tensor, starts: torch.Tensor, n_entries: int,
                           max_new: int, num_q_heads: int, window: int | None, keep_first: int, scale: float,
-                          gate: torch.Tensor | None, row_lo: int, status: torch.Tensor) -> None:
+                          gate: torch.Tensor | None, row_lo: int, status: torch.Tensor,
+                          distance_bias: torch.Tensor | None = None) -> None:
     """The tcgen05 prefill attention for the entries of a step with more than ``row_lo`` rows
     (new tokens x heads per kv head): ``q`` [N, heads * D] and ``out`` [N, heads * D] bfloat16,
     caches [pages, kv_heads, page_size, D].  ``window`` with ``keep_first``: keys below it
-    stay visible; ``gate`` (32-bit [N, >= heads]): sigmoid gates per (token, head)."""
+    stay visible; ``gate`` (32-bit [N, >= heads]): sigmoid gates per (token, head);
+    ``distance_bias`` (32-bit [heads, L]): entry min(query position - key position, L - 1) of the
+    head's row is added to the score before the scale, so it holds the bias over the scale."""
     _dense(q, "q"), _dense(out, "out"), _dense(k_cache, "k_cache"), _dense(v_cache, "v_cache"), _dense(block_table, "block_table")
     num_pages, nkv, page_size, d = k_cache.shape
     n = q.shape[0]
@@ -152,13 +158,16 @@ def attention_prefill_tc5(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
     fn = getattr(handle, f"fe_attention_prefill_tc5_d{d}")
     if not getattr(fn, "_declared", False):
         p, i, f, ll = c_void_p, c_int, c_float, ctypes.c_longlong
-        fn.argtypes = [p, i, p, p, p, p, i, i, i, i, i, p, p, i, i, i, i, i, f, p, ll, i, p, p]
+        fn.argtypes = [p, i, p, p, p, p, i, i, i, i, i, p, p, i, i, i, i, i, f, p, ll, i, p, i, p, p]
         fn.restype = c_int
         fn._declared = True
+    assert distance_bias is None or (distance_bias.dtype == torch.float32 and distance_bias.is_contiguous()
+                                     and distance_bias.dim() == 2 and distance_bias.shape[0] == num_q_heads)
     gate_stride = 0 if gate is None else (int(gate.stride(0)) if n > 1 else int(gate.shape[1]))
     check(fn(ptr(q), int(q.shape[1]), ptr(out), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.shape[1],
              page_size, num_pages, nkv, num_q_heads // nkv, ptr(cu_tokens), ptr(starts), int(n_entries), int(max_new), n,
-             int(window or 0), int(keep_first or 0), float(scale), ptr(gate), gate_stride, int(row_lo), ptr(status),
+             int(window or 0), int(keep_first or 0), float(scale), ptr(gate), gate_stride, int(row_lo),
+             ptr(distance_bias), 0 if distance_bias is None else int(distance_bias.shape[1]), ptr(status),
              stream()), "attention_prefill_tc5")
 
 
@@ -533,13 +542,17 @@ def bias_xielu(x: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, a_
 def gated_recurrence(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_bias: torch.Tensor | None,
                      lower: torch.Tensor, norm_weight: torch.Tensor, eps: float, state: torch.Tensor,
                      slots: torch.Tensor, cu_tokens: torch.Tensor, out: torch.Tensor, n_entries: int,
-                     status: torch.Tensor) -> None:
+                     status: torch.Tensor, max_new: int = 1) -> None:
     """The gated linear recurrence over the tokens of every entry, from and to the request's
     state row.  ``proj`` 32-bit [N, C] holds the sums of the q, f and v projections from
     columns ``q_off``, ``f_off`` and ``v_off`` on (heads x dk, heads x dk, heads x dv);
     q = silu(zq), f = lower + (1 - lower) sigmoid(zf + f_bias); ``state`` 32-bit
     [rows, heads, dk, dv]: S <- diag(f) S + (1 - f) v^T, o = S^T q, and ``out`` [N, heads * dv]
-    gets o / sqrt(mean_over_dv(o^2) + eps) * norm_weight per head."""
+    gets o / sqrt(mean_over_dv(o^2) + eps) * norm_weight per head.
+    ``max_new``: the most tokens an entry brings.  Entries of gated_recurrence_long_from() tokens
+    or more run chunk-parallel (chunks of 64 tokens side by side from a zero state, the chunks'
+    start states chained afterwards and added in, all in 32-bit) where the kernels' tiles fit
+    shared memory; shorter entries of the same step are walked token by token."""
     _dense(proj, "proj"), _dense(state, "state"), _dense(out, "out")
     rows, heads, dk, dv = state.shape
     assert proj.dtype == torch.float32 and state.dtype == torch.float32
@@ -548,10 +561,24 @@ def gated_recurrence(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_b
     assert norm_weight.dtype == torch.float32 and norm_weight.numel() == dv
     assert out.shape == (proj.shape[0], heads * dv) and slots.dtype == torch.int32 and cu_tokens.dtype == torch.int32
     assert max(q_off, f_off) + heads * dk <= proj.shape[1] and v_off + heads * dv <= proj.shape[1]
+    n = int(proj.shape[0])
+    scratch = None
+    if max_new >= gated_recurrence_long_from():
+        floats = int(lib().fe_gated_recurrence_scratch(n, int(n_entries), int(heads), int(dk), int(dv)))
+        if floats > 0:
+            scratch = _scratch.get("gated recurrence chunks", proj.device, floats, torch.float32, 1 << 22)
     check(lib().fe_gated_recurrence(ptr(proj), int(proj.shape[1]), int(q_off), int(f_off), int(v_off), ptr(f_bias),
                                     ptr(lower), ptr(norm_weight), float(eps), ptr(state), int(rows), ptr(slots),
                                     ptr(cu_tokens), ptr(out), code(out), int(n_entries), int(heads), int(dk), int(dv),
-                                    ptr(status), stream()), "gated_recurrence")
+                                    n, int(max_new), ptr(scratch), ptr(status), stream()), "gated_recurrence")
+    if scratch is not None:
+        global LAUNCHES
+        LAUNCHES += 3
+
+
+def gated_recurrence_long_from() -> int:
+    """Tokens from which on an entry of gated_recurrence runs chunk-parallel."""
+    return int(lib().fe_gated_recurrence_long_from())
 
 
 def add_normed_rmsnorm(residual: torch.Tensor, update: torch.Tensor | None, update_weight: torch.Tensor | None,

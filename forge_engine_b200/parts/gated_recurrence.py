@@ -59,7 +59,8 @@ class GatedRecurrence(Mixer):
         mixed = torch.empty((x.shape[0], self.h * self.dv), dtype=self.ctx.dtype, device=x.device)
         with self.ctx.section("mixer.recurrence"):
             native.gated_recurrence(proj, 0, qk, 2 * qk, self.f_bias, self.lower, self.norm, self.spec.norm_eps,
-                                    cache.state, batch.slots, batch.cu_tokens, mixed, batch.n_entries, self.ctx.status)
+                                    cache.state, batch.slots, batch.cu_tokens, mixed, batch.n_entries, self.ctx.status,
+                                    max_new=batch.max_new)
         return mixed
 
     def forward(self, x, batch, cache: CacheView):

@@ -31,6 +31,24 @@ def _mm_out_dtype_works(device) -> bool:
     return _MM_HAS_OUT_DTYPE
 
 
+_ADDMM_HAS_OUT_DTYPE: bool | None = None
+
+
+def _addmm_out_dtype_works(device) -> bool:
+    """Whether the library product takes a 32-bit bias row and leaves 32-bit sums for bfloat16
+    operands (asked once, with numbers whose sums are exact)."""
+    global _ADDMM_HAS_OUT_DTYPE
+    if _ADDMM_HAS_OUT_DTYPE is None:
+        try:
+            a = torch.ones((8, 16), dtype=torch.bfloat16, device=device)
+            bias = torch.arange(8, dtype=torch.float32, device=device) + 0.5
+            r = torch.addmm(bias, a, a.t(), out_dtype=torch.float32)
+            _ADDMM_HAS_OUT_DTYPE = r.dtype == torch.float32 and bool((r == bias + 16.0).all())
+        except Exception:
+            _ADDMM_HAS_OUT_DTYPE = False
+    return _ADDMM_HAS_OUT_DTYPE
+
+
 class Linear:
     """One projection.  ``weight`` is [out, in]; ``bias`` (optional) is kept in 32-bit."""
 
@@ -62,6 +80,8 @@ class Linear:
                 return torch.addmm(self._bias_model, x, self.weight.t())
             if self.bias is None and _mm_out_dtype_works(x.device):
                 return torch.mm(x, self.weight.t(), out_dtype=torch.float32)
+            if self.bias is not None and out_dtype == torch.float32 and _addmm_out_dtype_works(x.device):
+                return torch.addmm(self.bias, x, self.weight.t(), out_dtype=torch.float32)
         out = torch.empty((n, self.out_features), dtype=out_dtype, device=x.device)
         native.gemm_simt(x, self.weight, out, self.bias)
         return out

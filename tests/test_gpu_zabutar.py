@@ -432,8 +432,15 @@ def cuda_batch(counts, slots):
     return as_int(cu), as_int(entry), as_int(slots)
 
 
+SHORT_ENTRIES = {0: [19, 1, 2], 3: [1, 37, 1], 1: [2, 3, 40]}
+# entries long enough for the chunk-parallel kernels beside short ones: a chunk's length and
+# its neighbours, one token over a chunk, several chunks, a last chunk of one token
+LONG_ENTRIES = {0: [300, 1, 129], 3: [1, 128, 70], 1: [64, 127, 257]}
+
+
+@pytest.mark.parametrize("lengths", (SHORT_ENTRIES, LONG_ENTRIES), ids=("short", "long"))
 @pytest.mark.parametrize("heads, dk, dv", ((4, 8, 16), (3, 10, 12), (1, 64, 64), (2, 96, 128), (1, 200, 24), (5, 4, 4), (2, 48, 32)))
-def test_gated_recurrence_kernel(heads, dk, dv):
+def test_gated_recurrence_kernel(heads, dk, dv, lengths):
     """Entries of unequal lengths, carried over three calls from the state rows, against a
     loop over time; a slot that is zeroed and used again starts from nothing."""
     from forge_engine_b200.ops import native
@@ -446,7 +453,6 @@ def test_gated_recurrence_kernel(heads, dk, dv):
     eps = 1e-5
     state = torch.zeros(5, heads, dk, dv, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    lengths = {0: [19, 1, 2], 3: [1, 37, 1], 1: [2, 3, 40]}
     history = {slot: [] for slot in lengths}
     for call in range(3):
         counts = [lengths[slot][call] for slot in lengths]
@@ -455,7 +461,7 @@ def test_gated_recurrence_kernel(heads, dk, dv):
         cu, _, slots = cuda_batch(counts, list(lengths))
         out = torch.empty(n, v, device="cuda")
         native.gated_recurrence(proj.cuda(), 3, 3 + qk, 3 + 2 * qk, f_bias.cuda(), lower.cuda(), norm.cuda(), eps, state,
-                                slots, cu, out, len(counts), status)
+                                slots, cu, out, len(counts), status, max_new=max(counts))
         at = 0
         for slot, count in zip(lengths, counts):
             history[slot].append((proj[at : at + count].double(), out[at : at + count].cpu()))
