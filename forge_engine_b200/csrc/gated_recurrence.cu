@@ -144,10 +144,14 @@ __global__ void __launch_bounds__(1024) gated_recurrence_kernel(GatedRecurrence 
 }
 
 
-// One chunk of a long entry from a zero state (see the head of this file).
+// One chunk of a long entry from a zero state (see the head of this file).  A thread keeps the
+// rows s * kpt .. s * kpt + kpt - 1 of its column, so that it reads its gates and queries of a
+// token with 16-byte loads from shared memory; the rows up to KPT are padded with f = 1, q = 0
+// (such a row stays zero), and a pitch of KPT + 4 keeps the eight lanes of a load in different
+// banks.  The running product of the gates and q * b are the work of one thread per channel.
 template <int KPT>
 __global__ void __launch_bounds__(1024) gated_recurrence_local_kernel(GatedRecurrence p) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   pdl_trigger();
   pdl_wait();
   const int head = blockIdx.x, entry = blockIdx.y, chunk = blockIdx.z;
@@ -155,15 +159,21 @@ __global__ void __launch_bounds__(1024) gated_recurrence_local_kernel(GatedRecur
   if (entry_count < p.long_from || chunk * GR_LONG_CHUNK >= entry_count) return;
   const int first = entry_first + chunk * GR_LONG_CHUNK, count = min(GR_LONG_CHUNK, entry_count - chunk * GR_LONG_CHUNK);
   const int dk = p.dk, dv = p.dv, DS = p.ds, kpt = p.kpt;
-  float* fs = smem;                       // [GR_CHUNK][dk]
-  float* qs = fs + GR_CHUNK * dk;         // [GR_CHUNK][dk]
-  float* vs = qs + GR_CHUNK * dk;         // [GR_CHUNK][dv]
+  constexpr int KP = KPT >= 8 ? KPT + 4 : KPT;
+  const int pitch = DS * KP;              // floats per token
+  float* fs = smem;                       // [GR_CHUNK][DS][KP]
+  float* qs = fs + GR_CHUNK * pitch;      // [GR_CHUNK][DS][KP]
+  float* vs = qs + GR_CHUNK * pitch;      // [GR_CHUNK][dv]
+  float* bs = vs + GR_CHUNK * dv;         // [dk]: the product of the gates so far
   const int tid = threadIdx.x;
   const int v = tid / DS, s = tid - v * DS;
   const bool live = v < dv;
-  float S[KPT], B[KPT];                   // B: the product of the gates so far (kept by column 0's threads)
+  float S[KPT];
 #pragma unroll
-  for (int i = 0; i < KPT; ++i) { S[i] = 0.f; B[i] = 1.f; }
+  for (int i = 0; i < KPT; ++i) S[i] = 0.f;
+  for (int idx = tid; idx < GR_CHUNK * pitch; idx += blockDim.x) { fs[idx] = 1.f; qs[idx] = 0.f; }
+  for (int d = tid; d < dk; d += blockDim.x) bs[d] = 1.f;
+  __syncthreads();
   const float* bias = p.f_bias ? p.f_bias + head * dk : nullptr;
   const float* low = p.lower + head * dk;
   for (int c0 = 0; c0 < count; c0 += GR_CHUNK) {
@@ -174,30 +184,41 @@ __global__ void __launch_bounds__(1024) gated_recurrence_local_kernel(GatedRecur
       const float zq = row[p.q_off + head * dk + d];
       const float zf = row[p.f_off + head * dk + d] + (bias ? bias[d] : 0.f);
       const float l = low[d];
-      qs[idx] = zq * gr_sigmoid(zq);
-      fs[idx] = l + (1.f - l) * gr_sigmoid(zf);
+      const int owner = d / kpt, at = t * pitch + owner * KP + (d - owner * kpt);
+      qs[at] = zq * gr_sigmoid(zq);
+      fs[at] = l + (1.f - l) * gr_sigmoid(zf);
     }
     for (int idx = tid; idx < nt * dv; idx += blockDim.x) {
       const int t = idx / dv, c = idx - t * dv;
       vs[idx] = p.proj[(size_t)(first + c0 + t) * p.ld + p.v_off + head * dv + c];
     }
     __syncthreads();
+    for (int d = tid; d < dk; d += blockDim.x) {
+      const int owner = d / kpt, at = owner * KP + (d - owner * kpt);
+      float b = bs[d];
+      float* dst = p.qb + (size_t)(first + c0) * p.heads * dk + (size_t)head * dk + d;
+      for (int t = 0; t < nt; ++t) {
+        b *= fs[t * pitch + at];
+        dst[(size_t)t * p.heads * dk] = qs[t * pitch + at] * b;
+      }
+      bs[d] = b;
+    }
     for (int t = 0; t < nt; ++t) {
       const float vv = live ? vs[t * dv + v] : 0.f;
-      const float* ft = fs + t * dk + s;
-      const float* qt = qs + t * dk + s;
+      const float4* f4 = reinterpret_cast<const float4*>(fs + t * pitch + s * KP);
+      const float4* q4 = reinterpret_cast<const float4*>(qs + t * pitch + s * KP);
       float acc = 0.f;
 #pragma unroll
-      for (int i = 0; i < KPT; ++i) {
-        if (i < kpt) {
-          const float f = ft[i * DS];
-          S[i] = fmaf(f, S[i], (1.f - f) * vv);
-          acc = fmaf(S[i], qt[i * DS], acc);
-          if (v == 0) {
-            B[i] *= f;
-            p.qb[(size_t)(first + c0 + t) * p.heads * dk + (size_t)head * dk + i * DS + s] = qt[i * DS] * B[i];
-          }
-        }
+      for (int i = 0; i < KPT / 4; ++i) {
+        const float4 f = f4[i], q = q4[i];
+        S[4 * i + 0] = fmaf(f.x, S[4 * i + 0], (1.f - f.x) * vv);
+        S[4 * i + 1] = fmaf(f.y, S[4 * i + 1], (1.f - f.y) * vv);
+        S[4 * i + 2] = fmaf(f.z, S[4 * i + 2], (1.f - f.z) * vv);
+        S[4 * i + 3] = fmaf(f.w, S[4 * i + 3], (1.f - f.w) * vv);
+        acc = fmaf(S[4 * i + 0], q.x, acc);
+        acc = fmaf(S[4 * i + 1], q.y, acc);
+        acc = fmaf(S[4 * i + 2], q.z, acc);
+        acc = fmaf(S[4 * i + 3], q.w, acc);
       }
       for (int o = DS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (live && s == 0) p.o_local[(size_t)(first + c0 + t) * p.heads * dv + (size_t)head * dv + v] = acc;
@@ -206,10 +227,9 @@ __global__ void __launch_bounds__(1024) gated_recurrence_local_kernel(GatedRecur
   }
   const size_t at = (size_t)gr_chunk_slot(entry_first, entry, chunk) * p.heads + head;
 #pragma unroll
-  for (int i = 0; i < KPT; ++i) {
-    if (live && i < kpt) p.chunk_state[(at * dk + i * DS + s) * dv + v] = S[i];
-    if (v == 0 && i < kpt) p.chunk_decay[at * dk + i * DS + s] = B[i];
-  }
+  for (int i = 0; i < KPT; ++i)
+    if (live && i < kpt) p.chunk_state[(at * dk + s * kpt + i) * dv + v] = S[i];
+  for (int d = tid; d < dk; d += blockDim.x) p.chunk_decay[at * dk + d] = bs[d];
 }
 
 // One thread per element (d, v) of a head's state: the start state of every chunk of a long
@@ -244,9 +264,12 @@ __global__ void __launch_bounds__(256) gated_recurrence_scan_kernel(GatedRecurre
 }
 
 // o_t = (q_t * b_t)^T S_start + o_local_t for the tokens of one chunk, then the head's norm.
+// Thread (t, g) of 64 x 4 takes token t and, per round of 32 columns, the columns 4g .. 4g + 3
+// and 16 + 4g .. 16 + 4g + 3 (dv is a multiple of 4); S_start and q * b are read from shared
+// memory 16 bytes at a time.
 template <typename TO>
 __global__ void __launch_bounds__(256) gated_recurrence_finish_kernel(GatedRecurrence p) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   pdl_trigger();
   pdl_wait();
   const int head = blockIdx.x, entry = blockIdx.y, chunk = blockIdx.z;
@@ -254,37 +277,50 @@ __global__ void __launch_bounds__(256) gated_recurrence_finish_kernel(GatedRecur
   if (entry_count < p.long_from || chunk * GR_LONG_CHUNK >= entry_count) return;
   const int first = entry_first + chunk * GR_LONG_CHUNK, count = min(GR_LONG_CHUNK, entry_count - chunk * GR_LONG_CHUNK);
   const int dk = p.dk, dv = p.dv;
-  const int qld = dk + 1;                   // a warp's eight tokens read different banks
-  float* ss = smem;                         // [dk][dv]
-  float* qb = ss + dk * dv;                 // [GR_LONG_CHUNK][dk + 1]
+  const int dkp = (dk + 3) & ~3;            // rows in fours; the added ones are zero
+  const int qld = dkp + 4;                  // 16-byte rows; a warp's eight tokens read different banks
+  float* ss = smem;                         // [dkp][dv]
+  float* qb = ss + dkp * dv;                // [GR_LONG_CHUNK][qld]
   float* os = qb + GR_LONG_CHUNK * qld;     // [GR_LONG_CHUNK][dv]
   const int tid = threadIdx.x;
   const float* start = p.chunk_start + ((size_t)gr_chunk_slot(entry_first, entry, chunk) * p.heads + head) * dk * dv;
-  for (int i = tid; i < dk * dv; i += blockDim.x) ss[i] = start[i];
-  for (int i = tid; i < count * dk; i += blockDim.x) {
-    const int t = i / dk, d = i - t * dk;
-    qb[t * qld + d] = p.qb[(size_t)(first + t) * p.heads * dk + (size_t)head * dk + d];
+  for (int i = tid; i < dkp * dv; i += blockDim.x) ss[i] = i < dk * dv ? start[i] : 0.f;
+  for (int i = tid; i < count * qld; i += blockDim.x) {
+    const int t = i / qld, d = i - t * qld;
+    qb[i] = d < dk ? p.qb[(size_t)(first + t) * p.heads * dk + (size_t)head * dk + d] : 0.f;
   }
   __syncthreads();
-  // thread (t, g): token t, columns g, g + 4, g + 8, ... in rounds of eight columns
   const int t = tid >> 2, g = tid & 3;
   if (t < count) {
     const float* qt = qb + t * qld;
+    const float* local = p.o_local + (size_t)(first + t) * p.heads * dv + (size_t)head * dv;
     for (int v0 = 0; v0 < dv; v0 += 32) {
-      float acc[8];
+      const int c0 = v0 + 4 * g, c1 = c0 + 16;
+      const bool has0 = c0 < dv, has1 = c1 < dv;
+      float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+      for (int d = 0; d < dkp; d += 4) {
+        const float4 q = *reinterpret_cast<const float4*>(qt + d);
+        const float qk[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int d = 0; d < dk; ++d) {
-        const float q = qt[d];
-        const float* sr = ss + d * dv + v0 + g;
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (v0 + g + 4 * j < dv) acc[j] = fmaf(q, sr[4 * j], acc[j]);
+        for (int k = 0; k < 4; ++k) {
+          const float* sr = ss + (d + k) * dv;
+          if (has0) {
+            const float4 x = *reinterpret_cast<const float4*>(sr + c0);
+            a0.x = fmaf(qk[k], x.x, a0.x), a0.y = fmaf(qk[k], x.y, a0.y), a0.z = fmaf(qk[k], x.z, a0.z), a0.w = fmaf(qk[k], x.w, a0.w);
+          }
+          if (has1) {
+            const float4 x = *reinterpret_cast<const float4*>(sr + c1);
+            a1.x = fmaf(qk[k], x.x, a1.x), a1.y = fmaf(qk[k], x.y, a1.y), a1.z = fmaf(qk[k], x.z, a1.z), a1.w = fmaf(qk[k], x.w, a1.w);
+          }
+        }
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int v = v0 + g + 4 * j;
-        if (v < dv) os[t * dv + v] = acc[j] + p.o_local[(size_t)(first + t) * p.heads * dv + (size_t)head * dv + v];
+      if (has0) {
+        const float4 l = *reinterpret_cast<const float4*>(local + c0);
+        *reinterpret_cast<float4*>(os + t * dv + c0) = make_float4(a0.x + l.x, a0.y + l.y, a0.z + l.z, a0.w + l.w);
+      }
+      if (has1) {
+        const float4 l = *reinterpret_cast<const float4*>(local + c1);
+        *reinterpret_cast<float4*>(os + t * dv + c1) = make_float4(a1.x + l.x, a1.y + l.y, a1.z + l.z, a1.w + l.w);
       }
     }
   }
@@ -315,12 +351,15 @@ static int gr_column_threads(int dk, int dv) {
 }
 
 // Shared memory of gated_recurrence_finish, and whether the chunk-parallel kernels take these sizes.
-static size_t gr_finish_smem(int dk, int dv) { return sizeof(float) * ((size_t)dk * dv + (size_t)GR_LONG_CHUNK * (dk + 1 + dv)); }
+static size_t gr_finish_smem(int dk, int dv) {
+  const size_t dkp = (size_t)(dk + 3) / 4 * 4;
+  return sizeof(float) * (dkp * dv + (size_t)GR_LONG_CHUNK * (dkp + 4 + dv));
+}
 
 // 32-bit floats of scratch the chunk-parallel kernels need for a step of `tokens` tokens in
 // `entries` entries (0: these sizes run token by token whatever the entries' lengths).
 FE_EXPORT long long fe_gated_recurrence_scratch(int tokens, int entries, int heads, int dk, int dv) {
-  if (gr_finish_smem(dk, dv) > 200 * 1024 || gr_column_threads(dk, dv) == 0) return 0;
+  if (dv % 4 != 0 || gr_finish_smem(dk, dv) > 200 * 1024 || gr_column_threads(dk, dv) == 0) return 0;
   const long long slots = tokens / GR_LONG_CHUNK + entries + 1;
   return (long long)tokens * heads * (dk + dv) + slots * heads * ((long long)2 * dk * dv + dk);
 }
@@ -378,7 +417,8 @@ FE_EXPORT int fe_gated_recurrence(const float* proj, long long ld, int q_off, in
   if (rc || !chunked) return rc ? rc : fe_last_error();
   const int chunks = (max_new + GR_LONG_CHUNK - 1) / GR_LONG_CHUNK;
   if (chunks > 65535) return FE_ERR_TOO_LARGE;
-  const size_t local_smem = sizeof(float) * (size_t)GR_CHUNK * (2 * dk + dv);
+  const int kpt_built = kpt <= 4 ? 4 : kpt <= 8 ? 8 : kpt <= 16 ? 16 : 32;      // the instantiation's KPT, and its pitch
+  const size_t local_smem = sizeof(float) * ((size_t)GR_CHUNK * (2 * ds * (kpt_built >= 8 ? kpt_built + 4 : kpt_built) + dv) + dk);
 #define GR_LOCAL(KPT)                                                                                                  \
   do {                                                                                                                 \
     if (local_smem > 48 * 1024)                                                                                        \
