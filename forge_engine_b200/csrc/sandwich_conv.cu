@@ -5,6 +5,10 @@
 //                       (written back unless told otherwise), out = x * rsqrt(mean(x^2) + eps) * w.
 //                       Both norms and the sum are 32-bit; one rounding on store.  With a row map
 //                       only the mapped rows are produced (the model's last norm on wanted rows).
+//                       With a convolution's weights and state (a step in which every entry
+//                       brings one token: row r is entry r) the row goes straight through the
+//                       convolution below instead of being stored: the same arithmetic in the same
+//                       order as the two kernels one after the other.
 //   causal_conv_state   u_t = y_t + sum_j w[:, j] * y_(t - taps + 1 + j) per channel, over the tokens
 //                       of every entry of the step.  The taps - 1 rows of y before an entry's first
 //                       token come from the request's state row (zeros at a sequence's start), and
@@ -29,7 +33,8 @@ template <typename TU, typename TO, int V>
 __global__ void __launch_bounds__(256)
 add_normed_rmsnorm_kernel(float* __restrict__ residual, const TU* __restrict__ update, const float* __restrict__ w_update,
                           const float* __restrict__ weight, TO* __restrict__ out, const int* __restrict__ row_map, int size,
-                          float eps_update, float eps, int write_residual) {
+                          float eps_update, float eps, int write_residual, const float* __restrict__ conv_w,
+                          float* __restrict__ conv_state, long long state_stride, const int* __restrict__ slots, int taps) {
   extern __shared__ __align__(16) float row[];       // [size]
   __shared__ float scratch[33];
   pdl_trigger();
@@ -71,6 +76,37 @@ add_normed_rmsnorm_kernel(float* __restrict__ residual, const TU* __restrict__ u
   }
   const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)size + eps);
   TO* dst = out + (size_t)r * size;
+  if (conv_w != nullptr) {
+    // the entry's one token through the convolution: taps - 1 rows from the state, then this one
+    const int back = taps - 1;
+    float* st = back > 0 ? conv_state + (size_t)slots[r] * state_stride : nullptr;
+    for (int i = threadIdx.x * V; i < size; i += blockDim.x * V) {
+      float y[V], w[V], sum[V], hist[CONV_MAX_TAPS][V];
+      sc_load<V>(row + i, y), sc_load<V>(weight + i, w);
+#pragma unroll
+      for (int k = 0; k < V; ++k) y[k] = y[k] * inv * w[k], sum[k] = 0.f;
+#pragma unroll
+      for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+        if (j < taps) {
+          if (j < back) sc_load<V>(st + (size_t)j * size + i, hist[j]);
+          else {
+#pragma unroll
+            for (int k = 0; k < V; ++k) hist[j][k] = y[k];
+          }
+          sc_load<V>(conv_w + (size_t)j * size + i, w);
+#pragma unroll
+          for (int k = 0; k < V; ++k) sum[k] = fmaf(w[k], hist[j][k], sum[k]);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < V; ++k) sum[k] = y[k] + sum[k];
+      sc_store<V>(dst + i, sum);
+#pragma unroll
+      for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+        if (j < back) sc_store<V>(st + (size_t)j * size + i, hist[j + 1]);
+    }
+    return;
+  }
   for (int i = threadIdx.x * V; i < size; i += blockDim.x * V) {
     float x[V], w[V];
     sc_load<V>(row + i, x), sc_load<V>(weight + i, w);
@@ -81,19 +117,27 @@ add_normed_rmsnorm_kernel(float* __restrict__ residual, const TU* __restrict__ u
 }
 
 // residual 32-bit [*, size]; update [*, size] or null; w_update, weight 32-bit [size] (as they
-// multiply: any offset of a stored weight is already in them); out [rows, size]
+// multiply: any offset of a stored weight is already in them); out [rows, size].
+// conv_w (or null) 32-bit [taps, size], conv_state and slots as causal_conv_state takes them:
+// row r is then the one token of entry r, and out gets the convolution's result.
 FE_EXPORT int fe_add_normed_rmsnorm(float* residual, const void* update, int update_dtype, const float* w_update,
                                     const float* weight, void* out, int out_dtype, const int* row_map, int rows, int size,
-                                    float eps_update, float eps, int write_residual, cudaStream_t stream) {
+                                    float eps_update, float eps, int write_residual, const float* conv_w,
+                                    float* conv_state, long long state_stride, const int* slots, int taps,
+                                    cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (size < 1) return FE_ERR_BAD_SHAPE;
+  if (conv_w != nullptr && (taps < 1 || taps > CONV_MAX_TAPS || row_map != nullptr || slots == nullptr ||
+                            (taps > 1 && conv_state == nullptr)))
+    return FE_ERR_BAD_SHAPE;
   const size_t smem = (size_t)size * sizeof(float);
   if (smem > 200 * 1024) return FE_ERR_TOO_LARGE;
   int threads = 64;
   while (threads < 256 && threads * 8 < size) threads <<= 1;
   int rc = FE_ERR_BAD_DTYPE;
-  const bool wide = size % 4 == 0 && (((uintptr_t)residual | (uintptr_t)update | (uintptr_t)w_update | (uintptr_t)weight |
-                                       (uintptr_t)out) & 15) == 0;
+  const bool wide = size % 4 == 0 && (state_stride % 4) == 0 &&
+                    (((uintptr_t)residual | (uintptr_t)update | (uintptr_t)w_update | (uintptr_t)weight | (uintptr_t)out |
+                      (uintptr_t)conv_w | (uintptr_t)conv_state) & 15) == 0;
 #define LAUNCH_V(TU, TO, V)                                                                                            \
   do {                                                                                                                 \
     if (smem > 48 * 1024)                                                                                              \
@@ -101,7 +145,7 @@ FE_EXPORT int fe_add_normed_rmsnorm(float* residual, const void* update, int upd
                            (int)smem);                                                                                 \
     rc = fe_launch_dependent(add_normed_rmsnorm_kernel<TU, TO, V>, dim3(rows), dim3(threads), smem, stream, residual,  \
                              (const TU*)update, w_update, weight, (TO*)out, row_map, size, eps_update, eps,            \
-                             write_residual);                                                                          \
+                             write_residual, conv_w, conv_state, state_stride, slots, taps);                           \
   } while (0)
 #define LAUNCH(TU, TO)                                                                                                 \
   do {                                                                                                                 \

@@ -69,7 +69,7 @@ def _declare(handle: ctypes.CDLL) -> None:
         "fe_gated_recurrence": [p, ll, i, i, i, p, p, p, f, p, i, p, p, p, i, i, i, i, i, i, i, p, p, p],
         "fe_gated_recurrence_scratch": [i, i, i, i, i],
         "fe_gated_recurrence_long_from": [],
-        "fe_add_normed_rmsnorm": [p, p, i, p, p, p, i, p, i, i, f, f, i, p],
+        "fe_add_normed_rmsnorm": [p, p, i, p, p, p, i, p, i, i, f, f, i, p, p, ll, p, i, p],
         "fe_causal_conv_state": [p, p, p, ll, p, p, p, p, i, i, i, i, i, p],
         "fe_moe_route": [p, ll, i, i, i, i, i, p, p, p, p, p, p, p, p, p, i, i, i, p, i, i, f, f, p],
         "fe_moe_grouped": [p, i, ll, p, p, i, p, i, i, i, i, i, p, p, p, p, p, i, f, f, i, p],
@@ -583,11 +583,15 @@ def gated_recurrence_long_from() -> int:
 
 def add_normed_rmsnorm(residual: torch.Tensor, update: torch.Tensor | None, update_weight: torch.Tensor | None,
                        weight: torch.Tensor, out: torch.Tensor, eps_update: float, eps: float,
-                       row_map: torch.Tensor | None = None, write_residual: bool = True) -> None:
+                       row_map: torch.Tensor | None = None, write_residual: bool = True,
+                       conv: tuple | None = None) -> None:
     """residual (32-bit [N, C]) += update / sqrt(mean(update^2) + eps_update) * update_weight,
     then out = residual / sqrt(mean(residual^2) + eps) * weight; both weights 32-bit as they
     multiply.  Without ``update`` only the second norm runs.  With ``row_map`` only those rows
-    are produced (``write_residual`` False leaves the stream as it was)."""
+    are produced (``write_residual`` False leaves the stream as it was).
+    ``conv`` = (taps_weight, state, slots) as ``causal_conv_state`` takes them, for a step in
+    which every entry brings one token (row r is entry r): ``out`` then gets the convolution
+    of the normalised rows, bit for bit what the two kernels give one after the other."""
     _dense(residual, "residual"), _dense(out, "out")
     size = residual.shape[-1]
     rows = residual.shape[0] if row_map is None else row_map.numel()
@@ -597,9 +601,24 @@ def add_normed_rmsnorm(residual: torch.Tensor, update: torch.Tensor | None, upda
         _dense(update, "update")
         assert update.shape == residual.shape and update_weight is not None
         assert update_weight.dtype == torch.float32 and update_weight.numel() == size
+    conv_w = state = slots = None
+    taps = stride = 0
+    if conv is not None:
+        conv_w, state, slots = conv
+        _dense(conv_w, "taps_weight")
+        taps = int(conv_w.shape[0])
+        assert row_map is None and conv_w.dtype == torch.float32 and conv_w.shape[1] == size and slots.dtype == torch.int32
+        assert slots.numel() >= rows
+        if taps > 1:
+            assert state is not None and state.dtype == torch.float32 and state[0].is_contiguous()
+            assert state[0].numel() == (taps - 1) * size
+            stride = int(state.stride(0))
+        else:
+            state = None
     check(lib().fe_add_normed_rmsnorm(ptr(residual), ptr(update), code(update) if update is not None else F32,
                                       ptr(update_weight), ptr(weight), ptr(out), code(out), ptr(row_map), int(rows),
-                                      int(size), float(eps_update), float(eps), 1 if write_residual else 0, stream()),
+                                      int(size), float(eps_update), float(eps), 1 if write_residual else 0,
+                                      ptr(conv_w), ptr(state), stride, ptr(slots), taps, stream()),
           "add_normed_rmsnorm")
 
 

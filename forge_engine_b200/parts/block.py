@@ -303,11 +303,17 @@ class SandwichConvBlock:
             update, out_norm = pending
         elif pending is not None:
             h.add_(pending)              # a block of another arrangement handed a plain update on
+        u = torch.empty(h.shape, dtype=self.ctx.dtype, device=h.device)
+        state = None if cache.own_state is None else cache.own_state[:, sublayer]
+        if batch.max_new == 1 and batch.n_entries == h.shape[0]:
+            # every entry brings one token: norms, sum and convolution in one launch
+            native.add_normed_rmsnorm(h, update, None if out_norm is None else out_norm.weight, norm.weight, u,
+                                      0.0 if out_norm is None else out_norm.eps, norm.eps,
+                                      conv=(self.conv[sublayer], state, batch.slots))
+            return u
         y = torch.empty(h.shape, dtype=torch.float32, device=h.device)
         native.add_normed_rmsnorm(h, update, None if out_norm is None else out_norm.weight, norm.weight, y,
                                   0.0 if out_norm is None else out_norm.eps, norm.eps)
-        u = torch.empty(h.shape, dtype=self.ctx.dtype, device=h.device)
-        state = None if cache.own_state is None else cache.own_state[:, sublayer]
         native.causal_conv_state(y, self.conv[sublayer], state, batch.slots, batch.cu_tokens, batch.token_entry, u,
                                  batch.n_entries)
         return u

@@ -547,6 +547,50 @@ def test_activation_and_double_norm_kernels():
     assert float((out.cpu() - want.float()).abs().max()) <= 1e-5 * float(want.abs().max())
 
 
+@pytest.mark.parametrize("width", (40, 50, 37))
+@pytest.mark.parametrize("taps", (1, 2, 4, 8))
+@pytest.mark.parametrize("out_dtype", (torch.float32, torch.bfloat16))
+def test_norm_and_convolution_in_one_launch(taps, out_dtype, width):
+    """Steps in which every entry brings one token: the norms, the sum and the convolution in
+    one launch give bit for bit what the two kernels give one after the other, in the results,
+    the stream and the state, over several steps and with slots in any order; and both follow
+    the plain functions."""
+    from forge_engine_b200.ops import native
+
+    gen = torch.Generator().manual_seed(taps * 100 + width)
+    w = 0.5 * torch.randn(width, taps, generator=gen)
+    taps_weight = w.t().contiguous().cuda()
+    wb, wn = torch.randn(width, generator=gen), torch.randn(width, generator=gen)
+    order = [3, 0, 2]
+    slots = torch.tensor(order, dtype=torch.int32, device="cuda")
+    cu, entry, _ = cuda_batch([1, 1, 1], order)
+    states = [torch.zeros(4, 2, max(taps - 1, 1), width, device="cuda") for _ in range(2)]
+    streams = [torch.randn(3, width, generator=gen).cuda()] * 2
+    streams = [streams[0].clone(), streams[1].clone()]
+    rows_of = {slot: [] for slot in order}
+    for step in range(taps + 2):
+        upd = (3.0 * torch.randn(3, width, generator=gen)).cuda()
+        before = streams[0].cpu().double()
+        fused = torch.empty(3, width, dtype=out_dtype, device="cuda")
+        native.add_normed_rmsnorm(streams[0], upd, wb.cuda(), wn.cuda(), fused, 1e-3, 1e-6,
+                                  conv=(taps_weight, states[0][:, 1] if taps > 1 else None, slots))
+        y = torch.empty(3, width, device="cuda")
+        native.add_normed_rmsnorm(streams[1], upd, wb.cuda(), wn.cuda(), y, 1e-3, 1e-6)
+        apart = torch.empty(3, width, dtype=out_dtype, device="cuda")
+        native.causal_conv_state(y, taps_weight, states[1][:, 1] if taps > 1 else None, slots, cu, entry, apart, 3)
+        assert torch.equal(fused, apart) and torch.equal(streams[0], streams[1]) and torch.equal(states[0], states[1])
+        total = before + pz.rms(upd.cpu().double(), 1e-3) * wb.double()
+        normed = pz.rms(total, 1e-6) * wn.double()
+        for i, slot in enumerate(order):
+            rows_of[slot].append((normed[i], fused[i].float().cpu()))
+    for slot, pieces in rows_of.items():
+        want = pz.short_convolution(torch.stack([y for y, _ in pieces]), w.double())
+        got = torch.stack([o for _, o in pieces])
+        tol = 1e-5 if out_dtype == torch.float32 else 2e-2
+        assert float((got - want.float()).abs().max()) <= tol * max(1.0, float(want.abs().max()))
+    assert float(states[0][:, 0].abs().max()) == 0.0 and float(states[0][1].abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16))
 @pytest.mark.parametrize("experts, identity, top, groups, tokens, ff", (
     (5, 1, 2, (3, 2), 150, 32), (8, 4, 4, (3, 2), 300, 48), (6, 0, 2, (1, 1), 33, 24), (1, 3, 2, (2, 1), 40, 16),
