@@ -353,11 +353,13 @@ def loud_bias(weights: dict) -> None:
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv_heads, dim", ((2, 1, 16), (4, 2, 64)), ids=("heads of 16", "heads of 64"))
 @pytest.mark.parametrize("rows, far", ((12, 40), (8, 17.5), (32, 120), (4, 3), (6, 250)))
-def test_keys_at_the_edges_of_the_distance_buckets(tmp_path, rows, far, dtype):
-    """Every distance up to well past ``far`` occurs, in a prompt and for decoded tokens, with
-    a table that makes a wrong row show; the page size is not a divisor of any bucket's edge."""
-    cfg = pz.config([pz.attention_layer(heads=2, kv_heads=1, dim=16, vdim=16, bias_rows=rows, bias_max=far, mlp=None)], width=32)
+def test_keys_at_the_edges_of_the_distance_buckets(tmp_path, rows, far, dtype, heads, kv_heads, dim):
+    """Every distance up to well past ``far`` occurs, in a prompt (whole and in two portions)
+    and for decoded tokens, with a table that makes a wrong row show; the page size is not a
+    divisor of any bucket's edge.  Heads of 64 take the tensor-core prompt kernel in bfloat16."""
+    cfg = pz.config([pz.attention_layer(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, bias_rows=rows, bias_max=far, mlp=None)], width=32)
     weights = write_model(tmp_path / "m", cfg, 23, change=loud_bias)
     length = max(40, min(int(far * 1.3) + 12, 330))
     tokens = tokens_of(cfg, length, 12)
@@ -366,8 +368,10 @@ def test_keys_at_the_edges_of_the_distance_buckets(tmp_path, rows, far, dtype):
     whole = run_schedule(runner, {"a": tokens}, [[("a", length)]])["a"]
     head = length - 20
     decoded = run_schedule(runner, {"b": tokens}, [[("b", head)]] + [[("b", 1)] for _ in range(20)])["b"]
+    cut = run_schedule(runner, {"c": tokens}, [[("c", 13)], [("c", length - 13)]])["c"]
     assert_close(whole, ref, dtype, "prompt")
     assert_close(decoded, ref, dtype, "decoded")
+    assert_close(cut, ref, dtype, "two portions")
     # the table is what decides: with a flat table the logits are far from these
     flat = dict(weights)
     flat["l0.mix.rel"] = torch.zeros_like(weights["l0.mix.rel"])
@@ -376,12 +380,13 @@ def test_keys_at_the_edges_of_the_distance_buckets(tmp_path, rows, far, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dim", (16, 64))
 @pytest.mark.parametrize("new_tokens", (1, 0))
-def test_a_far_key_among_hundreds(tmp_path, new_tokens, dtype):
+def test_a_far_key_among_hundreds(tmp_path, new_tokens, dtype, dim):
     """One early key is made to stand out (its token's embedding and the last token's are
     scaled so that their score towers over the rest) and the table's last row favours far keys:
     the late logits rest on a key 300 tokens back, in a prompt and when decoding."""
-    cfg = pz.config([pz.attention_layer(heads=2, kv_heads=1, dim=16, vdim=16, bias_rows=8, bias_max=64, mlp=None)],
+    cfg = pz.config([pz.attention_layer(heads=2, kv_heads=1, dim=dim, vdim=dim, bias_rows=8, bias_max=64, mlp=None)],
                     width=32, vocab=50)
 
     def change(weights):
