@@ -86,7 +86,7 @@ def test_bad_values_are_refused(path, value):
         read_model_config(raw)
 
 
-@pytest.mark.parametrize("rows, far", ((12, 40), (32, 120), (8, 17.5), (2, 9), (4, 3), (6, 250), (64, 1000.5), (10, 5.01)))
+@pytest.mark.parametrize("rows, far", ((12, 40), (30, 140), (8, 17.5), (2, 9), (4, 3), (6, 250), (64, 1000.5), (10, 5.01)))
 def test_distance_bias_is_expanded_bucket_by_bucket(rows, far):
     from forge_engine_b200.parts.attention import GQAttention
 
