@@ -1,6 +1,7 @@
 """Configuration: part specs, the Qwen3 config, engine settings and the registry."""
 
 from .engine import EngineConfig, SchedulerConfig
+from .nuvivik import NuvivikConfig
 from .qwen3 import Qwen3Config
 from .registry import (
     Architecture,
@@ -22,6 +23,7 @@ from .specs import (
     ModelSpec,
     NoPositionSpec,
     NormSpec,
+    OutputNormSpec,
     RotarySpec,
     RoutedMLPSpec,
     RunSpec,
@@ -50,6 +52,11 @@ register_architecture(
     replace=True,
 )
 
+register_architecture(
+    Architecture("Nuvivik", NuvivikConfig.from_dict, NuvivikConfig.to_model_spec),
+    replace=True,
+)
+
 __all__ = [
     "Architecture",
     "AttentionSpec",
@@ -65,6 +72,8 @@ __all__ = [
     "ModelSpec",
     "NoPositionSpec",
     "NormSpec",
+    "NuvivikConfig",
+    "OutputNormSpec",
     "Qwen3Config",
     "RotarySpec",
     "RoutedMLPSpec",

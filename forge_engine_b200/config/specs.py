@@ -62,6 +62,14 @@ class RotarySpec:
     kind: str = "rope"
     # False: element j is paired with j + rotary_dim/2; True: element 2j with 2j + 1.
     interleaved: bool = False
+    # None, or (factor, low, high, original): frequencies are stretched by wavelength
+    # l = 2 pi / f.  Below original / high the frequency stays; above original / low it becomes
+    # f / factor; between the two, with s = (original / l - low) / (high - low), it becomes
+    # (1 - s) f / factor + s f.
+    scaling: tuple | None = None
+    # True: theta^(-2j / rotary_dim) is worked out in 64-bit and rounded once (always so with
+    # ``interleaved`` or ``scaling``); False: in 32-bit throughout, as Qwen3's own code does.
+    exact_frequencies: bool = False
 
 
 @dataclass(frozen=True)
@@ -122,6 +130,13 @@ class AttentionSpec:
     # False: the layer has no key and value projections; it reads another run's cache
     # (``RunSpec.cache_of``) with queries, bias and output projection of its own.
     kv_projection: bool = True
+    # With ``bias``: whether the output projection has one too (None: as q, k and v).
+    o_bias: bool | None = None
+    # False (per-head ``qk_norm`` only): q and k are divided by their root mean square and
+    # multiplied by no learned weight; the checkpoint holds no norm tensors.
+    qk_norm_weight: bool = True
+    # True (per-head ``qk_norm`` only): the norm is taken of the rotated head, not before the rotation.
+    qk_norm_after_rotation: bool = False
 
 
 @dataclass(frozen=True)
@@ -159,6 +174,11 @@ class LatentAttentionSpec:
     kv_from: int | None = None
     kind: str = "latent_attention"
     rename: tuple = ()
+    # None for full attention, else the number of most recent keys (the query's own included).
+    window: int | None = None
+    # True: tensor ``sink`` [heads]; exp(sink_h) joins the denominator of head h's softmax once,
+    # with no key and no value, neither scaled nor capped.
+    sink: bool = False
 
 
 @dataclass(frozen=True)
@@ -199,7 +219,9 @@ class GatedRecurrenceSpec:
 class DenseMLPSpec:
     """down(act(up(x) + b_up)) + b_down, no gate.  ``activation`` "xielu": with two learned
     numbers p, q (tensor ``act`` [2]) act(z) = softplus(p) z^2 + z / 2 above zero and
-    (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 at and below it."""
+    (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 at and below it; "gelu_tanh":
+    0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))); "relu2": max(z, 0)^2 (neither has tensors
+    of its own)."""
 
     hidden_size: int
     intermediate_size: int
@@ -226,7 +248,8 @@ class GatedMLPSpec:
 
 @dataclass(frozen=True)
 class RoutedMLPSpec:
-    """A routed feed-forward: ``experts`` gated units (``expert``: a GatedMLPSpec; tensors
+    """A routed feed-forward: ``experts`` units (``expert``: a GatedMLPSpec, or a DenseMLPSpec
+    without biases for units that have no gate; tensors
     ``e<i>.<name>``) of which every token uses the ``top`` with the largest router scores.
     ``score``: "sigmoid" or "softmax" of the router's 32-bit logits; ``renormalise``: the
     chosen scores are divided by their sum; ``weight_on`` "input": the unit runs on
@@ -257,6 +280,9 @@ class RoutedMLPSpec:
     # With ``renormalise``: weights = scores / (sum + renorm_floor); always times weight_scale.
     renorm_floor: float = 0.0
     weight_scale: float = 1.0
+    # What a group is worth: "max" - its largest choice score; "top2" - the sum of its two
+    # largest (of its one, where a group is a single expert).
+    group_score: str = "max"
 
 
 @dataclass(frozen=True)
@@ -308,6 +334,18 @@ class SandwichConvSpec:
 
 
 @dataclass(frozen=True)
+class OutputNormSpec:
+    """Options of the "output_norm" arrangement: a sublayer reads the residual stream as it
+    is and its output is normalised before it joins the stream, x += norm(sublayer(x)), for the
+    mixer and then for the feed-forward.  ``mixer_out_norm`` / ``ffn_out_norm``: the specs of
+    those norms (roles of the same names; the second is None for a layer without
+    feed-forward).  The layer has no ``input_norm`` and no ``post_norm``."""
+
+    mixer_out_norm: object = None
+    ffn_out_norm: object = None
+
+
+@dataclass(frozen=True)
 class RunSpec:
     """One entry of the order in which layers run.
 
@@ -345,3 +383,6 @@ class ModelSpec:
     # None, or the name of a tensor [max_positions, hidden]: row p is added to the embedding
     # of the token at position p.
     position_table_name: str | None = None
+    # logits = head(x) * logit_scale, then (with a cap c) c * tanh(logits / c)
+    logit_scale: float = 1.0
+    logit_softcap: float | None = None

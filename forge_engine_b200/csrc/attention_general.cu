@@ -26,6 +26,8 @@
 #define PREP_NORM_NONE 0
 #define PREP_NORM_HEAD 1     // every head over its first norm_dims elements, weight [norm_dims]
 #define PREP_NORM_WHOLE 2    // all heads at once, weight [heads * dim]
+#define PREP_NORM_HEAD_AFTER 3   // like PREP_NORM_HEAD, but taken of the rotated head (the rotation comes first)
+// A null weight in the per-head modes divides by the root mean square and multiplies by nothing.
 
 struct PrepSide {
   const void* in;      // token t's head h starts at in + t * in_stride + h * head_stride (elements)
@@ -43,22 +45,8 @@ __device__ __forceinline__ void prep_norm_rotate(float* row, const PrepSide& s, 
                                                  int rot_dims, int interleaved, float* scratch) {
   const int total = s.heads * s.dim;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-  if (s.norm_mode == PREP_NORM_WHOLE) {
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < total; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
-    const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)total + eps);
-    for (int i = threadIdx.x; i < total; i += blockDim.x) row[i] = row[i] * inv * s.norm_w[i];
-  } else if (s.norm_mode == PREP_NORM_HEAD) {
-    for (int h = warp; h < s.heads; h += warps) {
-      float* x = row + h * s.dim;
-      float ss = 0.f;
-      for (int i = lane; i < s.norm_dims; i += 32) ss = fmaf(x[i], x[i], ss);
-      const float inv = 1.f / sqrtf(warp_sum(ss) / (float)s.norm_dims + eps);
-      for (int i = lane; i < s.norm_dims; i += 32) x[i] = x[i] * inv * s.norm_w[i];
-    }
-  }
-  __syncthreads();
-  if (angles != nullptr && rot_dims > 0 && s.rot_off >= 0) {
+  const bool rotates = angles != nullptr && rot_dims > 0 && s.rot_off >= 0;
+  auto rotate = [&]() {
     const int half = rot_dims >> 1;
     for (int p = threadIdx.x; p < s.heads * half; p += blockDim.x) {
       const int h = p / half, j = p - h * half;
@@ -69,7 +57,39 @@ __device__ __forceinline__ void prep_norm_rotate(float* row, const PrepSide& s, 
       x[a] = u * cs.x - v * cs.y;
       x[b] = v * cs.x + u * cs.y;
     }
+  };
+  auto norm_heads = [&]() {
+    for (int h = warp; h < s.heads; h += warps) {
+      float* x = row + h * s.dim;
+      float ss = 0.f;
+      for (int i = lane; i < s.norm_dims; i += 32) ss = fmaf(x[i], x[i], ss);
+      const float inv = 1.f / sqrtf(warp_sum(ss) / (float)s.norm_dims + eps);
+      if (s.norm_w != nullptr) {
+        for (int i = lane; i < s.norm_dims; i += 32) x[i] = x[i] * inv * s.norm_w[i];
+      } else {
+        for (int i = lane; i < s.norm_dims; i += 32) x[i] = x[i] * inv;
+      }
+    }
+  };
+  if (s.norm_mode == PREP_NORM_HEAD_AFTER) {
+    if (rotates) {
+      rotate();
+      __syncthreads();
+    }
+    norm_heads();
+    __syncthreads();
+    return;
   }
+  if (s.norm_mode == PREP_NORM_WHOLE) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < total; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
+    const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)total + eps);
+    for (int i = threadIdx.x; i < total; i += blockDim.x) row[i] = row[i] * inv * s.norm_w[i];
+  } else if (s.norm_mode == PREP_NORM_HEAD) {
+    norm_heads();
+  }
+  __syncthreads();
+  if (rotates) rotate();
   __syncthreads();
 }
 
@@ -212,6 +232,8 @@ struct GeneralAttn {
   const float* gate;        // or null: the row (token, head) is multiplied by sigmoid(gate[token * gate_stride + head])
   long long gate_stride;
   int out_f32;              // the output is 32-bit whatever the cache holds
+  const float* sinks;       // or null: per query head a number whose exponential joins the softmax's
+                            //   denominator once (unscaled, uncapped), with no key and no value
 };
 
 // 1 + coef * ln(floor((p + 1) / every) + 1): what a query's scores are multiplied by
@@ -362,7 +384,9 @@ attention_general_kernel(GeneralAttn a, int* status) {
     float big = -INFINITY;
 #pragma unroll
     for (int w = 0; w < GA_WARPS; ++w) big = fmaxf(big, part_m[w * RMAX + r]);
-    float num = 0.f, den = 0.f;
+    const float sink = a.sinks ? a.sinks[head0 + r] : -INFINITY;
+    big = fmaxf(big, sink);
+    float num = 0.f, den = a.sinks ? expf(sink - big) : 0.f;
 #pragma unroll
     for (int w = 0; w < GA_WARPS; ++w) {
       const float pm = part_m[w * RMAX + r];
@@ -438,8 +462,8 @@ FE_EXPORT int fe_attention_general(const void* q, long long q_token_stride, long
                                    const float* dist_bias, int dist_len, int window,
                                    float scale, int keep_first, float softcap, float temp_coef, int temp_every,
                                    int parts, long long q_part_stride, int k_part_stride, long long o_part_stride,
-                                   const float* gate, long long gate_stride, int out_f32, int n_tokens, int* status,
-                                   cudaStream_t stream) {
+                                   const float* gate, long long gate_stride, int out_f32, const float* sinks,
+                                   int n_tokens, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (parts < 1) parts = 1;
   if (num_kv_heads < 1 || num_q_heads % num_kv_heads || (long long)num_kv_heads * parts > 65535) return FE_ERR_BAD_SHAPE;
@@ -448,7 +472,7 @@ FE_EXPORT int fe_attention_general(const void* q, long long q_token_stride, long
   GeneralAttn a{q, q_token_stride, q_head_stride, k_cache, k_row, k_dim, v_cache, v_row, v_dim, out, o_token_stride,
                 o_head_stride, block_table, max_pages, page_size, num_pages, num_kv_heads, num_q_heads, positions,
                 token_entry, slopes, dist_bias, dist_len, window, scale, keep_first, softcap, temp_coef, temp_every, parts, q_part_stride,
-                k_part_stride, o_part_stride, gate, gate_stride, out_f32};
+                k_part_stride, o_part_stride, gate, gate_stride, out_f32, sinks};
   if (dtype == FE_DTYPE_F32) return dispatch_general<float>(a, n_tokens, status, stream);
   if (dtype == FE_DTYPE_BF16) return dispatch_general<bf16>(a, n_tokens, status, stream);
   return FE_ERR_BAD_DTYPE;

@@ -56,6 +56,7 @@ struct Params {
   int parts; long long q_ps; int k_ps; long long o_ps;
   const float* gate; long long gate_stride; int out_f32;
   int row_hi;      // above zero: entries with more rows (new tokens x heads per kv head) are left to another kernel
+  const float* sinks;   // or null: per query head a number whose exponential joins the denominator once
 };
 
 __device__ __forceinline__ float query_temperature(int pos, float coef, int every) {
@@ -337,7 +338,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
       const int rho = row0 + rw * 16 + quad + 8 * h;
       const int token = t_begin + rho / p.groups, head = kvh * p.groups + rho % p.groups;
       const size_t at = (size_t)token * p.o_ts + (size_t)head * p.o_hs + (size_t)part * p.o_ps;
-      float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+      // a sink joins the normaliser in the units of the running maximum (log 2); one that dwarfs
+      // every score makes the sum infinite and the row zero, which is its limit
+      const float l_all = p.sinks ? l_run[h] + exp2f(p.sinks[head] * LOG2E - m_run[h]) : l_run[h];
+      float inv = l_all > 0.f ? 1.f / l_all : 0.f;
       if (p.gate) inv *= sigmoidf(p.gate[(size_t)token * p.gate_stride + head]);
       if (p.out_f32) {
         float* dst = reinterpret_cast<float*>(p.out) + at;
@@ -397,9 +401,15 @@ __global__ void __launch_bounds__(128) attention_mma_merge_kernel(Params p) {
       const float* row = base + ((size_t)lane * BM + r) * (DV + 2);
       const float m = lane < p.splits ? row[DV] : -INFINITY;
       const float l = lane < p.splits ? row[DV + 1] : 0.f;
-      const float big = warp_max(m);
+      float big = warp_max(m);
+      float sink = -INFINITY;      // counted once per row, here where the splits meet
+      if (p.sinks) {
+        const int rho = tile * BM + r;
+        sink = p.sinks[kvh * p.groups + rho % p.groups] * LOG2E;
+        big = fmaxf(big, sink);
+      }
       const float f = m == -INFINITY ? 0.f : exp2f(m - big);      // maxima are in units of log 2
-      const float den = warp_sum(l * f);
+      const float den = warp_sum(l * f) + (p.sinks ? exp2f(sink - big) : 0.f);
       if (lane < p.splits) weight[w][lane] = f;
       if (lane == 0) inverse[w] = den > 0.f ? 1.f / den : 0.f;
     }
@@ -437,8 +447,8 @@ FE_EXPORT int GM_NAME(fe_attention_gmma_)(const void* q, long long q_ts, long lo
                                           int window, float scale, int splits,
                                           float* workspace, int keep_first, float softcap, float temp_coef,
                                           int temp_every, int parts, long long q_ps, int k_ps, long long o_ps,
-                                          const float* gate, long long gate_stride, int out_f32, int row_hi, int* status,
-                                          cudaStream_t stream) {
+                                          const float* gate, long long gate_stride, int out_f32, int row_hi,
+                                          const float* sinks, int* status, cudaStream_t stream) {
   if (entries <= 0 || max_new <= 0) return 0;
   if (parts < 1) parts = 1;
   if (nkv < 1 || num_q_heads % nkv || (long long)nkv * parts > 65535 || entries > 65535) return FE_ERR_BAD_SHAPE;
@@ -454,7 +464,7 @@ FE_EXPORT int GM_NAME(fe_attention_gmma_)(const void* q, long long q_ts, long lo
   Params p{(const bf16*)q, q_ts, q_hs, (const bf16*)k_cache, k_row, (const bf16*)v_cache, v_row, out, o_ts, o_hs,
            block_table, max_pages, page_size, num_pages, nkv, groups, cu_tokens, starts, slopes, dist_bias, dist_len, window, scale,
            splits, tiles, workspace, keep_first, softcap, temp_coef, temp_every, parts, q_ps, k_ps, o_ps, gate,
-           gate_stride, out_f32, row_hi};
+           gate_stride, out_f32, row_hi, sinks};
   static bool configured = false;
   if (!configured) {
     const cudaError_t rc = cudaFuncSetAttribute(attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);

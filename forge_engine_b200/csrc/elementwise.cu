@@ -330,3 +330,69 @@ FE_EXPORT int fe_bias_xielu(const void* x, int x_dtype, const float* bias, void*
 #undef XIELU
   return rc ? rc : fe_last_error();
 }
+
+// ---------------------------------------------------------------------------
+// bias_act: out[n, i] = act(x[n, i] + bias[i]) for an activation of one argument, taken in
+// 32-bit of the projection's sums (bias 32-bit or null); one rounding on store.
+//   act 0: the tanh form of GELU, 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
+//   act 1: the square of relu
+// ---------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+bias_act_kernel(const TI* __restrict__ x, const float* __restrict__ bias, TO* __restrict__ out, long long total,
+                int width, int act) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    float z = to_float(x[i]);
+    if (bias != nullptr) z += bias[(int)(i % width)];
+    float v;
+    if (act == 1) {
+      const float r = fmaxf(z, 0.f);
+      v = r * r;
+    } else {
+      v = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    }
+    out[i] = from_float<TO>(v);
+  }
+}
+
+FE_EXPORT int fe_bias_act(const void* x, int x_dtype, const float* bias, void* out, int out_dtype, long long rows,
+                          int width, int act, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (width < 1 || act < 0 || act > 1) return FE_ERR_BAD_SHAPE;
+  const long long total = rows * width;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  int rc = FE_ERR_BAD_DTYPE;
+#define BIAS_ACT(TI, TO) \
+  rc = fe_launch_dependent(bias_act_kernel<TI, TO>, dim3((unsigned)blocks), dim3(256), 0, stream, (const TI*)x, bias, (TO*)out, total, width, act)
+  if (x_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32) BIAS_ACT(float, float);
+  else if (x_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_BF16) BIAS_ACT(float, bf16);
+  else if (x_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_BF16) BIAS_ACT(bf16, bf16);
+#undef BIAS_ACT
+  return rc ? rc : fe_last_error();
+}
+
+// ---------------------------------------------------------------------------
+// scale_cap: x <- x * scale, then (cap > 0) x <- cap * tanh(x / cap), in place on 32-bit values
+// (a model's logits).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) scale_cap_kernel(float* __restrict__ x, long long total, float scale, float cap) {
+  pdl_trigger();
+  pdl_wait();
+  const float inv = cap > 0.f ? 1.f / cap : 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    float v = x[i] * scale;
+    if (cap > 0.f) v = cap * tanhf(v * inv);
+    x[i] = v;
+  }
+}
+
+FE_EXPORT int fe_scale_cap(float* x, long long total, float scale, float cap, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  const int rc = fe_launch_dependent(scale_cap_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, total, scale, cap);
+  return rc ? rc : fe_last_error();
+}

@@ -38,7 +38,15 @@ constexpr int THREADS = 192;
 constexpr int CLUSTER_REDUCE_TOKENS = 128;
 
 enum Epilogue { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SILU_MUL_BF16 = 3, EPI_QKV_ROPE = 4, EPI_GELU_MUL_BF16 = 5,
-                EPI_CLAMP_MUL_BF16 = 6 };
+                EPI_CLAMP_MUL_BF16 = 6, EPI_RELU2_BF16 = 7, EPI_GELU_BF16 = 8 };
+
+// the epilogues that store an activation of each sum (+ bias), rounded once: the square of relu,
+// the tanh form of GELU
+__host__ __device__ constexpr bool is_unary(int epi) { return epi == EPI_RELU2_BF16 || epi == EPI_GELU_BF16; }
+template <int EPI> __device__ __forceinline__ float unary_act(float z) {
+  if (EPI == EPI_RELU2_BF16) { const float r = fmaxf(z, 0.f); return r * r; }
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
 
 // the epilogues that turn rows of alternating gate and up features into one gated value
 __host__ __device__ constexpr bool is_gated(int epi) {
@@ -150,7 +158,8 @@ __device__ __forceinline__ void store16(const GemmParams& p, float (&v)[16], int
     if (token >= p.n) break;
     const size_t at = (size_t)token * p.o + feature;
     const float r = v[j] + b;
-    if (EPI == EPI_STORE_BF16) reinterpret_cast<bf16*>(p.y)[at] = __float2bfloat16_rn(r);
+    if (is_unary(EPI)) reinterpret_cast<bf16*>(p.y)[at] = __float2bfloat16_rn(unary_act<EPI>(r));
+    else if (EPI == EPI_STORE_BF16) reinterpret_cast<bf16*>(p.y)[at] = __float2bfloat16_rn(r);
     else if (EPI == EPI_STORE_F32) reinterpret_cast<float*>(p.y)[at] = r;
     else reinterpret_cast<float*>(p.y)[at] = __ldcg(reinterpret_cast<const float*>(p.y) + at) + r;
   }
@@ -225,7 +234,8 @@ __device__ __forceinline__ void store_one(const GemmParams& p, float v, int feat
   if (feature >= p.o || token >= p.n) return;
   const size_t at = (size_t)token * p.o + feature;
   const float r = v + (p.bias ? p.bias[feature] : 0.f);
-  if (EPI == EPI_STORE_BF16) reinterpret_cast<bf16*>(p.y)[at] = __float2bfloat16_rn(r);
+  if (is_unary(EPI)) reinterpret_cast<bf16*>(p.y)[at] = __float2bfloat16_rn(unary_act<EPI>(r));
+  else if (EPI == EPI_STORE_BF16) reinterpret_cast<bf16*>(p.y)[at] = __float2bfloat16_rn(r);
   else if (EPI == EPI_STORE_F32) reinterpret_cast<float*>(p.y)[at] = r;
   else reinterpret_cast<float*>(p.y)[at] = __ldcg(reinterpret_cast<const float*>(p.y) + at) + r;
 }
@@ -587,6 +597,8 @@ int launch_bn(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p,
     case EPI_SILU_MUL_BF16: return launch_one<BN, EPI_SILU_MUL_BF16>(mw, mx, p, grid, stream);
     case EPI_GELU_MUL_BF16: return launch_one<BN, EPI_GELU_MUL_BF16>(mw, mx, p, grid, stream);
     case EPI_CLAMP_MUL_BF16: return launch_one<BN, EPI_CLAMP_MUL_BF16>(mw, mx, p, grid, stream);
+    case EPI_RELU2_BF16: return launch_one<BN, EPI_RELU2_BF16>(mw, mx, p, grid, stream);
+    case EPI_GELU_BF16: return launch_one<BN, EPI_GELU_BF16>(mw, mx, p, grid, stream);
     case EPI_QKV_ROPE:
       if (BN <= 64) return launch_one<(BN <= 64 ? BN : 16), EPI_QKV_ROPE>(mw, mx, p, grid, stream);
       return FE_ERR_BAD_SHAPE;
@@ -677,10 +689,12 @@ static int run_gemm(const void* x, const void* w, const float* bias, void* y, in
 // ksplit > 1 needs ws_part (floats: feature tiles * token tiles * ksplit * tile * 128) and
 // ws_count (one zeroed unsigned per output tile; left zeroed).
 // 6: y[n, o/2] = g' sigmoid(act_slope g') (u' + 1) with g' = min(gate, act_limit), u' = clamp(up, +-act_limit).
+// 7, 8: y[n, o] = act(sum + bias) in bfloat16, act the square of relu or the tanh form of GELU.
 FE_EXPORT int fe_gemm_tc5(const void* x, const void* w, const float* bias, void* y, int n, int o, int k,
                           int epilogue, int ksplit, float* ws_part, unsigned* ws_count, int* status,
                           float act_limit, float act_slope, cudaStream_t stream) {
-  if ((epilogue < EPI_STORE_BF16 || epilogue > EPI_SILU_MUL_BF16) && epilogue != EPI_GELU_MUL_BF16 && epilogue != EPI_CLAMP_MUL_BF16)
+  if ((epilogue < EPI_STORE_BF16 || epilogue > EPI_SILU_MUL_BF16) && epilogue != EPI_GELU_MUL_BF16 && epilogue != EPI_CLAMP_MUL_BF16 &&
+      !is_unary(epilogue))
     return FE_ERR_BAD_DTYPE;
   return run_gemm(x, w, bias, y, n, o, k, epilogue, ksplit, ws_part, ws_count, status, nullptr, stream, act_limit, act_slope);
 }
@@ -692,7 +706,7 @@ FE_EXPORT int fe_gemm_tc5(const void* x, const void* w, const float* bias, void*
 FE_EXPORT int fe_gemm_tc5_grouped(const void* x, const void* w, void* y, int slots, int experts, int o, int k, int epilogue,
                                   int tile_rows, int max_tiles, const int* tile_expert, const int* tile_row,
                                   const int* offsets, float act_limit, float act_slope, int* status, cudaStream_t stream) {
-  if (epilogue != EPI_STORE_BF16 && epilogue != EPI_STORE_F32 && !is_gated(epilogue)) return FE_ERR_BAD_DTYPE;
+  if (epilogue != EPI_STORE_BF16 && epilogue != EPI_STORE_F32 && !is_gated(epilogue) && !is_unary(epilogue)) return FE_ERR_BAD_DTYPE;
   if (tile_rows != 16 && tile_rows != 32 && tile_rows != 64 && tile_rows != 128) return FE_ERR_BAD_SHAPE;
   if (experts < 1 || max_tiles < 1 || max_tiles > 65535 || (long long)experts * o > 0x7fffffffLL) return FE_ERR_BAD_SHAPE;
   const Grouped grouped{experts, tile_rows, max_tiles, tile_expert, tile_row, offsets};

@@ -35,6 +35,14 @@
 
 struct MoeAct { int act; float limit, slope; };
 
+// what a product with one matrix applies to its sums: act 16 nothing, 17 the square of relu, 18 the tanh form of GELU
+#define MOE_UNARY 16
+__device__ __forceinline__ float moe_unary(float z, const MoeAct& a) {
+  if (a.act == MOE_UNARY + 1) { const float r = fmaxf(z, 0.f); return r * r; }
+  if (a.act == MOE_UNARY + 2) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z;
+}
+
 // the same gated units as act_mul's (0: SiLU, 1: tanh form of GELU, 2: the clamped unit)
 __device__ __forceinline__ float moe_act(float z, float u, const MoeAct& a) {
   if (a.act == 0) return z / (1.f + expf(-z)) * u;
@@ -114,6 +122,7 @@ struct MoeRouteExtras {
   int group_keep;           //   mark is its largest choice score, and only the best group_keep can be chosen
   float renorm_floor;       // with renormalise: weight = score / (sum of the chosen + renorm_floor)
   float weight_scale;       // every weight is multiplied by this
+  int group_top2;           // a group's mark is the sum of its two largest choice scores (of its one, in groups of one)
 };
 
 __global__ void __launch_bounds__(128)
@@ -142,8 +151,24 @@ moe_route_kernel(const float* __restrict__ logits, long long ld, int n_tokens, i
   if (x.group_count > 0) {
     for (int g = 0; g < x.group_count; ++g) {
       float mark = -INFINITY;
-      for (int e = g * per_group + lane; e < (g + 1) * per_group; e += 32) mark = fmaxf(mark, choice_of(e));
-      mark = warp_max(mark);
+      int mark_e = -1;
+      for (int e = g * per_group + lane; e < (g + 1) * per_group; e += 32) {
+        const float c = choice_of(e);
+        if (c > mark) { mark = c; mark_e = e; }
+      }
+      const float first = warp_max(mark);
+      const bool holds_first = mark == first && mark_e >= 0;      // this lane's best is the group's largest
+      mark = first;
+      if (x.group_top2 && per_group > 1) {
+        // the largest is left out at its lowest index (equal scores elsewhere still count), then the largest of the rest
+        int first_e = holds_first ? mark_e : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) first_e = min(first_e, __shfl_xor_sync(0xffffffffu, first_e, o));
+        float second = -INFINITY;
+        for (int e = g * per_group + lane; e < (g + 1) * per_group; e += 32)
+          if (e != first_e) second = fmaxf(second, choice_of(e));
+        mark = first + warp_max(second);
+      }
       if (lane == 0) group_mark[warp][g] = mark;
     }
     __syncwarp();
@@ -373,7 +398,7 @@ __global__ void __launch_bounds__(256) moe_grouped_kernel(MoeProduct p) {
     for (int j = 0; j < 4; ++j) {
       const int c = col0 + tx * 4 + j;
       if (c >= p.n) continue;
-      const float v = DUAL ? moe_act(acc[0][i][j], acc[DUAL ? 1 : 0][i][j], p.act) : acc[0][i][j];
+      const float v = DUAL ? moe_act(acc[0][i][j], acc[DUAL ? 1 : 0][i][j], p.act) : moe_unary(acc[0][i][j], p.act);
       out[(size_t)(row0 + r) * p.n + c] = from_float<TY>(v);
     }
   }
@@ -502,7 +527,7 @@ __global__ void __launch_bounds__(128) moe_grouped_mma_kernel(MoeProduct p) {
       for (int c = 0; c < 2; ++c) {
         const int col = col0 + j * 8 + pair * 2 + c;
         if (col >= p.n) continue;
-        const float v = DUAL ? moe_act(acc[0][j][2 * h + c], acc[DUAL ? 1 : 0][j][2 * h + c], p.act) : acc[0][j][2 * h + c];
+        const float v = DUAL ? moe_act(acc[0][j][2 * h + c], acc[DUAL ? 1 : 0][j][2 * h + c], p.act) : moe_unary(acc[0][j][2 * h + c], p.act);
         out[(size_t)(row0 + r) * p.n + col] = from_float<TY>(v);
       }
     }
@@ -584,7 +609,7 @@ FE_EXPORT int fe_moe_route(const float* logits, long long ld, int n_tokens, int 
                            int renormalise, int* counts, int* slot_expert, float* slot_weight, int* slot_rank,
                            int* slot_row, int* row_slot, int* offsets, int* tile_expert, int* tile_row, int max_tiles,
                            int tile_rows, int identity, const float* correction, int group_count, int group_keep,
-                           float renorm_floor, float weight_scale, cudaStream_t stream) {
+                           float renorm_floor, float weight_scale, int group_top2, cudaStream_t stream) {
   if (tile_rows <= 0) tile_rows = MOE_BM;
   if (n_tokens <= 0) return 0;
   if (identity < 0) return FE_ERR_BAD_SHAPE;
@@ -597,7 +622,7 @@ FE_EXPORT int fe_moe_route(const float* logits, long long ld, int n_tokens, int 
   // with identity units the tables have one more expert: the one that stands for all of them
   const int listed = experts + (identity > 0 ? 1 : 0);
   if ((size_t)(listed + 1) * sizeof(int) > 160 * 1024) return FE_ERR_TOO_LARGE;
-  MoeRouteExtras extras{identity, correction, group_count, group_keep, renorm_floor, weight_scale};
+  MoeRouteExtras extras{identity, correction, group_count, group_keep, renorm_floor, weight_scale, group_top2};
   int rc = fe_launch_dependent(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, logits, ld, n_tokens,
                                experts, top, softmax_scores, renormalise, extras, slot_expert, slot_weight, slot_rank, counts);
   if (rc) return rc;

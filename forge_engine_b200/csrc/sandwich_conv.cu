@@ -74,8 +74,18 @@ add_normed_rmsnorm_kernel(float* __restrict__ residual, const TU* __restrict__ u
       sc_store<V>(row + i, x);
     }
   }
-  const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)size + eps);
   TO* dst = out + (size_t)r * size;
+  if (weight == nullptr) {
+    // no norm of the stream: the sublayer reads the sum itself
+    __syncthreads();
+    for (int i = threadIdx.x * V; i < size; i += blockDim.x * V) {
+      float x[V];
+      sc_load<V>(row + i, x);
+      sc_store<V>(dst + i, x);
+    }
+    return;
+  }
+  const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)size + eps);
   if (conv_w != nullptr) {
     // the entry's one token through the convolution: taps - 1 rows from the state, then this one
     const int back = taps - 1;

@@ -177,4 +177,9 @@ class DecoderModel:
             else:
                 normed = self.final_norm.add_forward(h, pending, row_map=batch.want_rows)
         with self.ctx.section("head"):
-            return self.head(normed, out_dtype=torch.float32)
+            logits = self.head(normed, out_dtype=torch.float32)
+            scale, cap = float(getattr(self.spec, "logit_scale", 1.0)), getattr(self.spec, "logit_softcap", None)
+            if scale != 1.0 or cap is not None:
+                # logits * scale, then cap * tanh(. / cap): in place on the 32-bit logits
+                native.scale_cap(logits, scale, cap)
+            return logits

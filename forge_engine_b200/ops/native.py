@@ -63,15 +63,17 @@ def _declare(handle: ctypes.CDLL) -> None:
         "fe_qkv_prepare": [p, i, i, i, i, i, i, p, i, p, i, i, i, i, i, p, i, p, i, i, i, f, p, i, i, p, ll, ll, i,
                            p, p, i, p, i, i, i, p, p, i, p, p],
         "fe_attention_general": [p, ll, ll, p, i, i, p, i, i, p, ll, ll, i, p, i, i, i, i, i, p, p, p, p, i, i, f,
-                                 i, f, f, i, i, ll, i, ll, p, ll, i, i, p, p],
+                                 i, f, f, i, i, ll, i, ll, p, ll, i, p, i, p, p],
         "fe_differential_combine": [p, p, i, ll, i, f, f, f, p],
         "fe_bias_xielu": [p, i, p, p, i, ll, i, f, f, p],
+        "fe_bias_act": [p, i, p, p, i, ll, i, i, p],
+        "fe_scale_cap": [p, ll, f, f, p],
         "fe_gated_recurrence": [p, ll, i, i, i, p, p, p, f, p, i, p, p, p, i, i, i, i, i, i, i, p, p, p],
         "fe_gated_recurrence_scratch": [i, i, i, i, i],
         "fe_gated_recurrence_long_from": [],
         "fe_add_normed_rmsnorm": [p, p, i, p, p, p, i, p, i, i, f, f, i, p, p, ll, p, i, p],
         "fe_causal_conv_state": [p, p, p, ll, p, p, p, p, i, i, i, i, i, p],
-        "fe_moe_route": [p, ll, i, i, i, i, i, p, p, p, p, p, p, p, p, p, i, i, i, p, i, i, f, f, p],
+        "fe_moe_route": [p, ll, i, i, i, i, i, p, p, p, p, p, p, p, p, p, i, i, i, p, i, i, f, f, i, p],
         "fe_moe_grouped": [p, i, ll, p, p, i, p, i, i, i, i, i, p, p, p, p, p, i, f, f, i, p],
         "fe_moe_combine": [p, p, p, i, i, p, i, p, ll, p, i, i, p, i, p, i, p],
         "fe_moe_max_tiles": [i, i, i],
@@ -440,6 +442,7 @@ def gemm_tc5_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilog
     gated = epilogue in (TC5_SILU_MUL, TC5_GELU_MUL, TC5_CLAMP_MUL)
     assert out.shape == (slots, o // 2 if gated else o)
     assert out.dtype == (torch.float32 if epilogue == TC5_STORE_F32 else torch.bfloat16)
+    # epilogues 7 and 8 (``TC5_UNARY``) store an activation of one argument of every sum
     check(lib().fe_gemm_tc5_grouped(ptr(x), ptr(w), ptr(out), int(slots), int(experts), int(o), int(k), int(epilogue),
                                     int(tile_rows), int(max_tiles), ptr(plan["tile_expert"]), ptr(plan["tile_row"]),
                                     ptr(plan["offsets"]), float(limit), float(slope), ptr(status), stream()),
@@ -449,7 +452,7 @@ def gemm_tc5_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilog
 def moe_route(logits: torch.Tensor, experts: int, top: int, softmax: bool, renormalise: bool, counts: torch.Tensor,
               ints: torch.Tensor, slot_weight: torch.Tensor, max_tiles: int, tile_rows: int = 0, *,
               identity: int = 0, correction: torch.Tensor | None = None, groups: tuple | None = None,
-              renorm_floor: float = 0.0, weight_scale: float = 1.0) -> dict:
+              renorm_floor: float = 0.0, weight_scale: float = 1.0, group_top2: bool = False) -> dict:
     """Choose ``top`` of ``experts`` per token from 32-bit ``logits`` [N, >= experts] and lay
     the (token, choice) slots out by expert.  ``counts`` int32 [experts + 1] must be zero (it is
     zero again afterwards); ``ints`` is int32 scratch of at least 4 * N * top + experts + 2 +
@@ -459,7 +462,8 @@ def moe_route(logits: torch.Tensor, experts: int, top: int, softmax: bool, renor
     a slot that chose one gets expert number ``experts`` (rows, but no tiles).  ``correction``
     (32-bit [experts + identity]) is added to the scores for the choice only.  ``groups``
     (count, keep): the outputs form ``count`` equal groups of neighbours and only those of the
-    ``keep`` groups with the largest choice score can be chosen.  Weights are the chosen scores
+    ``keep`` groups with the largest choice score (``group_top2``: with the largest sum of their
+    two largest choice scores) can be chosen.  Weights are the chosen scores
     (divided by their sum + ``renorm_floor`` with ``renormalise``) times ``weight_scale``."""
     n = logits.shape[0]
     slots = n * top
@@ -481,7 +485,8 @@ def moe_route(logits: torch.Tensor, experts: int, top: int, softmax: bool, renor
                              ptr(views["slot_expert"]), ptr(slot_weight), ptr(views["slot_rank"]), ptr(views["slot_row"]),
                              ptr(views["row_slot"]), ptr(views["offsets"]), ptr(views["tile_expert"]),
                              ptr(views["tile_row"]), int(max_tiles), int(tile_rows), int(identity), ptr(correction),
-                             int(group_count), int(group_keep), float(renorm_floor), float(weight_scale), stream()), "moe_route")
+                             int(group_count), int(group_keep), float(renorm_floor), float(weight_scale),
+                             1 if group_top2 else 0, stream()), "moe_route")
     global LAUNCHES
     LAUNCHES += 1
     return views
@@ -493,7 +498,8 @@ def moe_grouped(a: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor | None, out:
     """One product over rows grouped by expert.  ``w1`` (and ``w2``) [experts, n, k];
     ``gather``: ``a`` holds the tokens' activations [N, k] and a sorted row reads its slot's
     token, times ``slot_weight`` when given; else ``a`` holds sorted rows [slots, k].  With
-    ``w2``: out = act(a w1^T, a w2^T) (see ``act_mul``), else out = a w1^T."""
+    ``w2``: out = act(a w1^T, a w2^T) (see ``act_mul``), else out = a w1^T, or an activation of
+    one argument of it when ``act`` is one of ``MOE_UNARY``'s codes."""
     _dense(a, "a"), _dense(w1, "w1"), _dense(out, "out")
     experts, n, k = w1.shape
     assert a.shape[1] == k and out.shape[1] == n and (w2 is None or (w2.shape == w1.shape and w2.dtype == w1.dtype))
@@ -537,6 +543,28 @@ def bias_xielu(x: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, a_
     assert out.shape == x.shape and (bias is None or (bias.dtype == torch.float32 and bias.numel() == width))
     check(lib().fe_bias_xielu(ptr(x), code(x), ptr(bias), ptr(out), code(out), rows, width, float(a_pos), float(a_neg),
                               stream()), "bias_xielu")
+
+
+UNARY_GELU_TANH, UNARY_RELU2 = 0, 1      # activations of one argument (``bias_act``)
+TC5_UNARY = {UNARY_RELU2: 7, UNARY_GELU_TANH: 8}      # -> epilogue of the tcgen05 product that stores act(sum + bias) in bfloat16
+MOE_UNARY = {None: 16, UNARY_RELU2: 17, UNARY_GELU_TANH: 18}   # -> what ``moe_grouped`` applies to a single product's sums
+
+
+def bias_act(x: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, act: int) -> None:
+    """out = act(x + bias) for an activation of one argument (``UNARY_GELU_TANH``: the tanh form
+    of GELU; ``UNARY_RELU2``: the square of relu), taken in 32-bit, one rounding on store.
+    ``bias`` 32-bit [C] or None."""
+    _dense(x, "x"), _dense(out, "out")
+    rows, width = x.shape
+    assert out.shape == x.shape and (bias is None or (bias.dtype == torch.float32 and bias.numel() == width))
+    check(lib().fe_bias_act(ptr(x), code(x), ptr(bias), ptr(out), code(out), rows, width, int(act), stream()), "bias_act")
+
+
+def scale_cap(x: torch.Tensor, scale: float, cap: float | None) -> None:
+    """In place on 32-bit values: x <- x * scale, then with a cap x <- cap * tanh(x / cap)."""
+    _dense(x, "x")
+    assert x.dtype == torch.float32
+    check(lib().fe_scale_cap(ptr(x), x.numel(), float(scale), float(cap or 0.0), stream()), "scale_cap")
 
 
 def gated_recurrence(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_bias: torch.Tensor | None,
@@ -587,7 +615,8 @@ def add_normed_rmsnorm(residual: torch.Tensor, update: torch.Tensor | None, upda
                        conv: tuple | None = None) -> None:
     """residual (32-bit [N, C]) += update / sqrt(mean(update^2) + eps_update) * update_weight,
     then out = residual / sqrt(mean(residual^2) + eps) * weight; both weights 32-bit as they
-    multiply.  Without ``update`` only the second norm runs.  With ``row_map`` only those rows
+    multiply.  Without ``update`` only the second norm runs; without ``weight`` (None) there is no
+    second norm and out = residual, rounded to ``out``'s dtype.  With ``row_map`` only those rows
     are produced (``write_residual`` False leaves the stream as it was).
     ``conv`` = (taps_weight, state, slots) as ``causal_conv_state`` takes them, for a step in
     which every entry brings one token (row r is entry r): ``out`` then gets the convolution
@@ -595,8 +624,8 @@ def add_normed_rmsnorm(residual: torch.Tensor, update: torch.Tensor | None, upda
     _dense(residual, "residual"), _dense(out, "out")
     size = residual.shape[-1]
     rows = residual.shape[0] if row_map is None else row_map.numel()
-    assert residual.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == size
-    assert out.shape == (rows, size)
+    assert residual.dtype == torch.float32 and (weight is None or (weight.dtype == torch.float32 and weight.numel() == size))
+    assert out.shape == (rows, size) and (weight is not None or conv is None)
     if update is not None:
         _dense(update, "update")
         assert update.shape == residual.shape and update_weight is not None
@@ -655,6 +684,7 @@ def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out
 
 
 PREP_NORM_NONE, PREP_NORM_HEAD, PREP_NORM_WHOLE = 0, 1, 2
+PREP_NORM_HEAD_AFTER = 3      # per head like PREP_NORM_HEAD, but of the rotated head: the rotation comes first
 
 
 def qkv_prepare(
@@ -690,7 +720,8 @@ def qkv_prepare(
 
     ``q`` [N, >= q_heads * q_dim] and ``k``, ``v`` may be column slices of one contiguous
     projection output (row stride taken from the tensor).  ``q_norm`` / ``k_norm`` =
-    (mode, leading elements of a head that are normalised, 32-bit weight): per head or over
+    (mode, leading elements of a head that are normalised, 32-bit weight): per head (before the
+    rotation, or with ``PREP_NORM_HEAD_AFTER`` after it; the weight may be None) or over
     the whole projection.  ``table`` [N, rot_dims / 2, 2] holds cosine and sine of the
     tokens' angles; elements [rot_off, rot_off + rot_dims) of every head are rotated (a
     negative ``rot_off`` leaves that side as it is), neighbours paired when ``interleaved``,
@@ -712,7 +743,7 @@ def qkv_prepare(
     assert table is None or (table.dtype == torch.float32 and table.is_contiguous() and table.shape == (n, rot_dims // 2, 2))
     for mode, dims, w in (q_norm, k_norm):
         assert w is None or (w.dtype == torch.float32 and w.is_cuda and w.is_contiguous())
-        assert mode == PREP_NORM_NONE or w is not None
+        assert mode != PREP_NORM_WHOLE or w is not None     # the per-head norms take no weight as a weight of ones
     stride = lambda t: 0 if t is None else int(t.stride(0)) if n > 1 else int(t.shape[1])  # noqa: E731
     pages = 0 if k_cache is None else k_cache.shape[0]
     check(
@@ -750,7 +781,7 @@ def general_attention_lib(key_dim: int, value_dim: int, value_in_key: bool):
         run = getattr(handle, f"fe_attention_gmma_{suffix}")
         p, i, f, ll = c_void_p, c_int, c_float, ctypes.c_longlong
         run.argtypes = [p, ll, ll, p, i, p, i, p, ll, ll, p, i, i, i, i, i, p, p, i, i, p, p, i, i, f, i, p,
-                        i, f, f, i, i, ll, i, ll, p, ll, i, i, p, p]
+                        i, f, f, i, i, ll, i, ll, p, ll, i, i, p, p, p]
         run.restype = c_int
         space = getattr(handle, f"fe_attention_gmma_workspace_{suffix}")
         space.argtypes = [i, i, i, i, i]
@@ -810,8 +841,12 @@ def attention_general(
     gate: torch.Tensor | None = None,
     row_hi: int = 0,
     distance_bias: torch.Tensor | None = None,
+    sinks: torch.Tensor | None = None,
 ) -> None:
     """Paged causal attention for any key and value size: scores, softmax and sums in 32-bit.
+
+    ``sinks`` (32-bit, per query head): exp(sink) joins the softmax's denominator once - a
+    weight that belongs to no key and no value, neither scaled nor capped.
 
     ``entries = (cu_tokens, starts, number of entries, most new tokens of an entry)`` lets
     bfloat16 calls whose sizes are multiples of 16 run on the tensor-core kernel (``splits``
@@ -842,6 +877,7 @@ def attention_general(
     assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == n and gate.shape[1] >= num_q_heads)
     assert distance_bias is None or (distance_bias.dtype == torch.float32 and distance_bias.is_cuda and distance_bias.is_contiguous()
                                      and distance_bias.dim() == 2 and distance_bias.shape[0] == num_q_heads)
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_cuda and sinks.is_contiguous() and sinks.numel() == num_q_heads)
     dist_len = 0 if distance_bias is None else int(distance_bias.shape[1])
     out_f32 = 1 if out.dtype == torch.float32 and q.dtype != torch.float32 else 0
     coef, every = query_temperature or (0.0, 0)
@@ -862,7 +898,7 @@ def attention_general(
             run(ptr(q), int(q_strides[0]), int(q_strides[1]), ptr(k_cache), k_row, ptr(v_cache), v_row, ptr(out),
                 int(o_strides[0]), int(o_strides[1]), ptr(block_table), block_table.shape[1], page_size, num_pages, nkv,
                 int(num_q_heads), ptr(cu_tokens), ptr(starts), int(n_entries), int(max_new), ptr(slopes),
-                ptr(distance_bias), dist_len, int(window or 0), float(scale), int(splits), ptr(workspace), *extras, int(row_hi), ptr(status), stream()),
+                ptr(distance_bias), dist_len, int(window or 0), float(scale), int(splits), ptr(workspace), *extras, int(row_hi), ptr(sinks), ptr(status), stream()),
             "attention_general (tensor cores)",
         )
         if splits > 1:
@@ -875,7 +911,7 @@ def attention_general(
             ptr(q), int(q_strides[0]), int(q_strides[1]), ptr(k_cache), k_row, int(k_dim), ptr(v_cache), v_row,
             int(v_dim), ptr(out), int(o_strides[0]), int(o_strides[1]), code(q), ptr(block_table),
             block_table.shape[1], page_size, num_pages, nkv, int(num_q_heads), ptr(positions), ptr(token_entry),
-            ptr(slopes), ptr(distance_bias), dist_len, int(window or 0), float(scale), *extras, n, ptr(status), stream(),
+            ptr(slopes), ptr(distance_bias), dist_len, int(window or 0), float(scale), *extras, ptr(sinks), n, ptr(status), stream(),
         ),
         "attention_general",
     )
@@ -1315,7 +1351,8 @@ def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int,
     epilogue 0: out bf16 [n, o]; 1: out f32 [n, o]; 2: out f32 [n, o] += product;
     3: out bf16 [n, o/2] = silu(gate) * up for w whose rows alternate 16 gate, 16 up features
     (5: the same with the tanh form of GELU; 6: g' sigmoid(slope g') (u' + 1) with g' = min(gate,
-    limit), u' = clamp(up, -limit, limit)).
+    limit), u' = clamp(up, -limit, limit)); 7, 8 (``TC5_UNARY``): out bf16 [n, o] = the square of
+    relu, or the tanh form of GELU, of the 32-bit sum + bias.
     ``ksplit`` blocks share an output tile (deterministic reduction through a workspace)."""
     _dense(x, "x"), _dense(w, "w"), _dense(out, "out")
     n, k = x.shape
@@ -1325,7 +1362,7 @@ def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int,
         assert out.shape == (n, o // 2) and out.dtype == torch.bfloat16
     else:
         assert out.shape == (n, o)
-        assert out.dtype == (torch.bfloat16 if epilogue == TC5_STORE_BF16 else torch.float32)
+        assert out.dtype == (torch.bfloat16 if epilogue == TC5_STORE_BF16 or epilogue in TC5_UNARY.values() else torch.float32)
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == o)
     part = count = None
     ksplit = max(1, min(int(ksplit), -(-k // 64)))

@@ -133,14 +133,16 @@ class GQAttention(Mixer):
     def _is_general(spec) -> bool:
         """Whether the layer needs what only the general kernels do: values of another size
         than keys, q and k normalised over the whole projection, a bias on the distance, kept
-        first tokens, capped scores, a query temperature, a gate per head, two maps per head."""
+        first tokens, capped scores, a query temperature, a gate per head, two maps per head, q and
+        k normalised without a weight or after the rotation."""
         return (getattr(spec, "v_head_dim", None) not in (None, spec.head_dim)
                 or (spec.qk_norm and getattr(spec, "qk_norm_scope", "head") == "whole")
                 or getattr(spec, "distance_bias_base", None) is not None
                 or getattr(spec, "distance_bias_table", None) is not None or not getattr(spec, "kv_projection", True)
                 or bool(getattr(spec, "keep_first", 0)) or getattr(spec, "softcap", None) is not None
                 or getattr(spec, "query_temperature", None) is not None or bool(getattr(spec, "head_gate", False))
-                or getattr(spec, "differential", None) is not None)
+                or getattr(spec, "differential", None) is not None
+                or (spec.qk_norm and (not getattr(spec, "qk_norm_weight", True) or getattr(spec, "qk_norm_after_rotation", False))))
 
     def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
         self.general = self._is_general(spec)
@@ -190,10 +192,13 @@ class GQAttention(Mixer):
             vectors = [weights[name(n)].float() for n in ("lambda_q1", "lambda_k1", "lambda_q2", "lambda_k2")]
             first, second = (vectors[0] * vectors[1]).sum(), (vectors[2] * vectors[3]).sum()
             self.diff_lambda = float((torch.exp(first) - torch.exp(second)).item() + float(self.differential.offset))
-        self.o_proj = Linear(weights[name("o_proj.weight")], weights[name("o_proj.bias")] if spec.bias else None,
+        self.o_proj = Linear(weights[name("o_proj.weight")], weights[name("o_proj.bias")] if self._o_bias(spec) else None,
                              status=ctx.status)
         self.q_norm = self.k_norm = None
-        if spec.qk_norm:
+        whole = getattr(spec, "qk_norm_scope", "head") == "whole"
+        if spec.qk_norm and whole and (not getattr(spec, "qk_norm_weight", True) or getattr(spec, "qk_norm_after_rotation", False)):
+            raise ConfigError("a norm over the whole projection has a weight and comes before the rotation")
+        if spec.qk_norm and getattr(spec, "qk_norm_weight", True):
             self.q_norm = weights[name("q_norm.weight")].float().contiguous()
             self.k_norm = weights[name("k_norm.weight")].float().contiguous()
         self.position = build_part(spec.position, {}, ctx)
@@ -214,6 +219,12 @@ class GQAttention(Mixer):
         self.plan_key = ("gqa_attention", self.nq, self.nkv, self.d, spec.window) + (
             ("general", self.dv, self.parts, self.keep_first) if self.general else ())
         self.last_splits = None   # what the last step's decode entries ran with (0: balanced kernel)
+
+    @staticmethod
+    def _o_bias(spec) -> bool:
+        """Whether the output projection has a bias: as q, k and v unless the spec says otherwise."""
+        wish = getattr(spec, "o_bias", None)
+        return bool(spec.bias) if wish is None else bool(wish)
 
     @staticmethod
     def expand_distance_bias(stored: torch.Tensor, far: float) -> torch.Tensor:
@@ -257,7 +268,7 @@ class GQAttention(Mixer):
         if parts > 1:
             for vector in ("lambda_q1", "lambda_k1", "lambda_q2", "lambda_k2"):
                 shapes[name(vector)] = WeightInfo((spec.head_dim,), "bias")
-        if spec.qk_norm:
+        if spec.qk_norm and getattr(spec, "qk_norm_weight", True):
             whole = getattr(spec, "qk_norm_scope", "head") == "whole"
             shapes[name("q_norm.weight")] = WeightInfo((q if whole else spec.head_dim,), "norm")
             shapes[name("k_norm.weight")] = WeightInfo((kv if whole else spec.head_dim,), "norm")
@@ -265,6 +276,7 @@ class GQAttention(Mixer):
             shapes[name("q_proj.bias")] = WeightInfo((q,), "bias")
             shapes[name("k_proj.bias")] = WeightInfo((kv,), "bias")
             shapes[name("v_proj.bias")] = WeightInfo((spec.num_kv_heads * dv,), "bias")
+        if cls._o_bias(spec):
             shapes[name("o_proj.bias")] = WeightInfo((h,), "bias")
         return shapes
 
@@ -338,6 +350,8 @@ class GQAttention(Mixer):
             mode = native.PREP_NORM_NONE
             if self.spec.qk_norm:
                 mode = native.PREP_NORM_WHOLE if self.spec.qk_norm_scope == "whole" else native.PREP_NORM_HEAD
+                if getattr(self.spec, "qk_norm_after_rotation", False):
+                    mode = native.PREP_NORM_HEAD_AFTER
             q = torch.empty((n, nq * d), dtype=k_cache.dtype, device=x.device)
             q_end, k_end = nq * d, (nq + nkv) * d
             if not self.kv_projection and cache.owns:

@@ -6,7 +6,9 @@ tensor updated in place; the block returns its last update *unadded* so that the
 block's first norm (or the final norm) adds it in the same kernel that normalises.
 
 "stream_mix" is the same pre-norm block over several copies of the residual stream that
-learned weights mix (or over one, with the update scaled by a constant).
+learned weights mix (or over one, with the update scaled by a constant).  "sandwich_conv" has
+a norm on both sides of every sublayer and a short convolution on its input; "output_norm" a
+norm on the sublayer's output only, the sublayer reading the stream itself.
 """
 
 from __future__ import annotations
@@ -345,3 +347,99 @@ class SandwichConvBlock:
 
 
 register_arrangement("sandwich_conv", SandwichConvBlock, replace=True)
+
+
+class OutputNormBlock:
+    """Sublayers that read the residual stream as it is and whose output is normalised before
+    it joins the stream: x += norm_a(mixer(x)), then x += norm_b(ff(x)) if the layer has a
+    feed-forward.  The stream ``h`` is 32-bit.  A sublayer's update is handed on unadded,
+    together with the norm that still has to be taken of it; one kernel launch normalises it,
+    adds it and writes the sum once more in the activation dtype, which is what the next
+    sublayer's projections read (in the 32-bit engine an exact copy).  The model's last norm
+    takes the pending update along through ``close``.  Updates are kept as the 32-bit sums of
+    the sublayer's last projection where the part can give them."""
+
+    roles = ("mixer", "mixer_out_norm", "ffn", "ffn_out_norm")
+
+    def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
+        self.ctx = ctx
+        options = spec.options
+        self.mixer = build_part(spec.mixer, weights["mixer"], ctx)
+        self.mixer_out_norm = build_part(options.mixer_out_norm, weights["mixer_out_norm"], ctx)
+        self.ffn = self.ffn_out_norm = None
+        if spec.ffn is not None:
+            self.ffn = build_part(spec.ffn, weights["ffn"], ctx)
+            self.ffn_out_norm = build_part(options.ffn_out_norm, weights["ffn_out_norm"], ctx)
+
+    @classmethod
+    def weight_shapes(cls, spec) -> dict:
+        """role -> {local name -> WeightInfo}"""
+        options = spec.options
+        shapes = {"mixer": part_class(spec.mixer).weight_shapes(spec.mixer),
+                  "mixer_out_norm": part_class(options.mixer_out_norm).weight_shapes(options.mixer_out_norm)}
+        if spec.ffn is not None:
+            shapes["ffn"] = part_class(spec.ffn).weight_shapes(spec.ffn)
+            shapes["ffn_out_norm"] = part_class(options.ffn_out_norm).weight_shapes(options.ffn_out_norm)
+        return shapes
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def plan_step(self, entries: list, page_size: int, plans: dict) -> None:
+        planner = getattr(self.mixer, "plan_step", None)
+        if planner is not None:
+            planner(entries, page_size, plans)
+
+    @property
+    def graph_safe(self) -> bool:
+        parts = [self.mixer, self.mixer_out_norm] + ([self.ffn, self.ffn_out_norm] if self.ffn is not None else [])
+        return all(getattr(part, "graph_safe", False) for part in parts)
+
+    def _enter(self, h, pending):
+        """Add what is pending (normalised) and hand the stream on in the activation dtype."""
+        update = out_norm = None
+        if isinstance(pending, tuple):
+            update, out_norm = pending
+        elif pending is not None:
+            h.add_(pending)              # a block of another arrangement handed a plain update on
+        u = torch.empty(h.shape, dtype=self.ctx.dtype, device=h.device)
+        native.add_normed_rmsnorm(h, update, None if out_norm is None else out_norm.weight, None, u,
+                                  0.0 if out_norm is None else out_norm.eps, 0.0)
+        return u
+
+    def _mix(self, u, batch, cache):
+        """The mixer's update, as the 32-bit sums of its output projection where it has one."""
+        attend, o_proj = getattr(self.mixer, "attend", None), getattr(self.mixer, "o_proj", None)
+        if attend is None or o_proj is None:
+            return self.mixer.forward(u, batch, cache)
+        heads = attend(u, batch, cache)
+        with self.ctx.section("mixer.o_proj"):
+            return o_proj(heads, out_dtype=torch.float32)
+
+    def forward(self, h, pending, batch, cache: CacheView):
+        with self.ctx.section("input_norm"):
+            u = self._enter(h, pending)
+        with self.ctx.section("mixer"):
+            update = self._mix(u, batch, cache)
+        pending = (update, self.mixer_out_norm)
+        if self.ffn is None:
+            return pending
+        with self.ctx.section("post_norm"):
+            u = self._enter(h, pending)
+        with self.ctx.section("ffn"):
+            update = self.ffn.forward(u)
+        return (update, self.ffn_out_norm)
+
+    def close(self, h, pending, final_norm, row_map):
+        """The model's last step: the pending update is normalised and added and the final norm
+        taken, for the rows of ``row_map`` only and without writing the stream."""
+        update, out_norm = pending if isinstance(pending, tuple) else (pending, None)
+        if out_norm is None:
+            return final_norm.add_forward(h, update, row_map=row_map)
+        normed = torch.empty((row_map.numel(), h.shape[-1]), dtype=self.ctx.dtype, device=h.device)
+        native.add_normed_rmsnorm(h, update, out_norm.weight, final_norm.weight, normed, out_norm.eps, final_norm.eps,
+                                  row_map=row_map, write_residual=False)
+        return normed
+
+
+register_arrangement("output_norm", OutputNormBlock, replace=True)

@@ -5,6 +5,8 @@ gate and up are one fused projection; the activation product is one kernel."""
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..config.specs import local_name
@@ -72,45 +74,62 @@ class GatedMLP(FeedForward):
         return self.down(act)
 
 
+UNARY = {"gelu_tanh": native.UNARY_GELU_TANH, "relu2": native.UNARY_RELU2}
+
+
 class DenseMLP(FeedForward):
-    """down(act(up(x) + b_up)) + b_down without a gate.  The activation is taken of the
-    projection's 32-bit sums plus the bias, in 32-bit, and rounded once.
+    """down(act(up(x) + b_up)) + b_down without a gate (biases optional).  The activation is
+    taken of the projection's 32-bit sums plus the bias, in 32-bit, and rounded once.
 
     "xielu": act(z) = a_pos z^2 + z / 2 for z > 0 and a_neg (exp(z) - 1 - z) + z / 2 otherwise,
     with a_pos = softplus(p) and a_neg = 1/2 + softplus(q) from the two learned numbers
-    ``act`` = (p, q), worked out once when the layer is built."""
+    ``act`` = (p, q), worked out once when the layer is built.  "gelu_tanh" (the tanh form of
+    GELU) and "relu2" (the square of relu) have no tensors; for steps of few tokens they are
+    the epilogue of the up projection's tcgen05 product."""
 
     graph_safe = True
 
     def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
-        if spec.activation != "xielu":
-            raise ConfigError(f"activation {spec.activation!r} is not implemented; known: xielu")
+        if spec.activation != "xielu" and spec.activation not in UNARY:
+            raise ConfigError(f"activation {spec.activation!r} is not implemented; known: xielu, {', '.join(UNARY)}")
         self.ctx = ctx
         self.inter = spec.intermediate_size
+        self.unary = UNARY.get(spec.activation)
         name = lambda canonical: local_name(spec, canonical)  # noqa: E731
         self.up = Linear(weights[name("up_proj.weight")], status=ctx.status)
         self.up_bias = weights[name("up_proj.bias")].to(device=ctx.device, dtype=torch.float32).contiguous() if spec.bias else None
         self.down = Linear(weights[name("down_proj.weight")], weights[name("down_proj.bias")] if spec.bias else None,
                            status=ctx.status)
-        p, q = (float(v) for v in weights[name("act")].double().cpu())
-        softplus = lambda z: float(torch.nn.functional.softplus(torch.tensor(z, dtype=torch.float64), threshold=1e9))  # noqa: E731
-        self.a_pos, self.a_neg = softplus(p), 0.5 + softplus(q)
+        self.a_pos = self.a_neg = 0.0
+        if self.unary is None:
+            p, q = (float(v) for v in weights[name("act")].double().cpu())
+            softplus = lambda z: float(torch.nn.functional.softplus(torch.tensor(z, dtype=torch.float64), threshold=1e9))  # noqa: E731
+            self.a_pos, self.a_neg = softplus(p), 0.5 + softplus(q)
 
     @classmethod
     def weight_shapes(cls, spec) -> dict:
         h, i = spec.hidden_size, spec.intermediate_size
         name = lambda canonical: local_name(spec, canonical)  # noqa: E731
-        shapes = {name("up_proj.weight"): WeightInfo((i, h)), name("down_proj.weight"): WeightInfo((h, i)),
-                  name("act"): WeightInfo((2,), "small")}
+        shapes = {name("up_proj.weight"): WeightInfo((i, h)), name("down_proj.weight"): WeightInfo((h, i))}
+        if spec.activation == "xielu":
+            shapes[name("act")] = WeightInfo((2,), "small")
         if spec.bias:
             shapes[name("up_proj.bias")] = WeightInfo((i,), "bias")
             shapes[name("down_proj.bias")] = WeightInfo((h,), "bias")
         return shapes
 
     def forward(self, x):
-        sums = self.up(x, out_dtype=torch.float32)
         act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        native.bias_xielu(sums, self.up_bias, act, self.a_pos, self.a_neg)
+        if self.unary is not None and self.up._tc5_ok(x) and os.environ.get("FORGE_ENGINE_UNARY_EPILOGUE", "1") != "0":
+            # few tokens: the activation is the product's own epilogue (32-bit sums + bias, one rounding)
+            native.gemm_tc5(x, self.up.weight, act, native.TC5_UNARY[self.unary], self.ctx.status, bias=self.up_bias,
+                            ksplit=native.tc5_ksplit(self.up.out_features, self.up.in_features))
+            return self.down(act, out_dtype=torch.float32)
+        sums = self.up(x, out_dtype=torch.float32)
+        if self.unary is None:
+            native.bias_xielu(sums, self.up_bias, act, self.a_pos, self.a_neg)
+        else:
+            native.bias_act(sums, self.up_bias, act, self.unary)
         return self.down(act, out_dtype=torch.float32)
 
 

@@ -14,6 +14,10 @@ and whose value is its first kv_rank elements, and the weighted sum of latents i
 W_uv,h afterwards.  A step's cost does not depend on how many heads read the cache.
 
 A layer with ``kv_from`` has no W_dkv and reads the cache of the layer named there.
+
+``window``: a query sees its own and the window - 1 tokens before it, and the pages the window
+has passed go back to the pool.  ``sink``: a learned number per head whose exponential joins
+the softmax's denominator once, as a weight on no key and no value.
 """
 
 from __future__ import annotations
@@ -53,7 +57,11 @@ class LatentAttention(Mixer):
         self.o_proj = Linear(weights[name("o")], status=ctx.status)
         self.position = build_part(spec.position, {}, ctx)
         self.rot_dims = self.position.rotary()[1]
-        self.plan_key = ("latent_attention", self.h, self.kv_rank, self.r)
+        self.window = getattr(spec, "window", None) or None
+        self.sinks = None
+        if getattr(spec, "sink", False):
+            self.sinks = weights[name("sink")].to(device=ctx.device, dtype=torch.float32).contiguous()
+        self.plan_key = ("latent_attention", self.h, self.kv_rank, self.r, self.window)
 
     def plan_step(self, entries: list, page_size: int, plans: dict) -> None:
         """The host's decision for a step of ``entries`` ((slot, cached, new) each): how many
@@ -61,7 +69,7 @@ class LatentAttention(Mixer):
         if self.plan_key not in plans:
             splits = 1
             if native.general_mma_takes(self.ctx.dtype, self.kv_rank + self.r, self.kv_rank):
-                splits = native.general_splits(entries, self.h, 1, None)
+                splits = native.general_splits(entries, self.h, 1, self.window)
             plans[self.plan_key] = splits
 
     @classmethod
@@ -79,10 +87,12 @@ class LatentAttention(Mixer):
         shapes[name("uk")] = WeightInfo((h * spec.head_dim, spec.kv_rank))
         shapes[name("uv")] = WeightInfo((h * spec.v_head_dim, spec.kv_rank))
         shapes[name("o")] = WeightInfo((w, h * spec.v_head_dim))
+        if getattr(spec, "sink", False):
+            shapes[name("sink")] = WeightInfo((h,), "bias")
         return shapes
 
     def cache_needs(self) -> CacheNeeds:
-        return CacheNeeds(kv=PagedKVSpec(1, self.kv_rank + self.r, None, 0))
+        return CacheNeeds(kv=PagedKVSpec(1, self.kv_rank + self.r, self.window, 0))
 
     def forward(self, x, batch, cache: CacheView):
         out = self.attend(x, batch, cache)
@@ -136,10 +146,10 @@ class LatentAttention(Mixer):
             self.plan_step(batch.entries, latent_cache.shape[2], batch.plans)
         with self.ctx.section("mixer.attention"):
             native.attention_general(q_eff, (h * (rank + r), rank + r), latent_cache, rank + r, latent_cache, rank,
-                                     mixed, (h * rank, rank), table, batch.positions, batch.token_entry, h, None, None,
+                                     mixed, (h * rank, rank), table, batch.positions, batch.token_entry, h, None, self.window,
                                      self.spec.scale, self.ctx.status,
                                      entries=(batch.cu_tokens, batch.starts, batch.n_entries, batch.max_new),
-                                     splits=batch.plans[self.plan_key])
+                                     splits=batch.plans[self.plan_key], sinks=self.sinks)
         heads = torch.empty((n, h, dv), dtype=dtype, device=x.device)
         with self.ctx.section("mixer.expand"):
             self._per_head(mixed, self.uv, heads)
