@@ -537,7 +537,8 @@ def design_compare(args) -> int:
     """Prefill (one 2,048-token prompt) and decode (batch 8, 2,048-token contexts) of models
     of `--layers` (4) layers of one kind: the Qwen3 layer, the Zofadra attention, latent
     attention and linear-recurrence layers, the Tekilorn differential, gated window and
-    routed layers and the Zabutar gated-recurrence, biased-attention and routed layers at the same sizes, plus a model of each design that mixes its layers.
+    routed layers, the Zabutar gated-recurrence, biased-attention and routed layers and the Nuvivik
+    attention, latent and routed layers at the same sizes, plus a model of each design that mixes its layers.
     One JSON line per model: tokens/s, ms per step, the median device time of every part of a
     step (CUDA events round each part, in a second runner) and, for the token-mixing kernel,
     its share of the measured peaks (prefill: its flops over the library GEMM's burst rate;
@@ -632,6 +633,32 @@ def design_compare(args) -> int:
             "zabutar-mixed": zabutar([z_recurrence, dict(z_recurrence, mlp=z_routed), z_attention,
                                       dict(z_attention, mixer=dict(z_attention["mixer"], kv_from=2), mlp=z_routed)]),
         })
+        # Nuvivik at the same sizes: windowed attention with biases, half the head rotated with
+        # stretched frequencies, the norm after the rotation and capped scores at Qwen3's head
+        # sizes; the latent layer at the Zofadra latent's sizes with the same window and a sink per
+        # head; the dense feed-forward (two matrices, no gate) of 3 ff / 2, so that it holds as many
+        # weights as the gated one of ff; a routed one with as many active weights per token (2 of
+        # 16 experts of 3 ff / 4 in 4 groups of which 2 are kept)
+        n_dense = {"kind": "dense", "ff": z["ff"] * 3 // 2}
+        n_routed = {"kind": "moe", "expert": {"ff": z["ff"] * 3 // 4},
+                    "router": {"experts": 16, "top": 2, "groups": {"count": 4, "keep": 2}}}
+        n_attention = {"type": "attention", "mlp": n_dense, "mixer": {
+            "heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "softcap": 30.0, "mask": {"size": window},
+            "rot": {"base": 1e6, "dims": D // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+        n_latent = {"type": "latent_attention", "mlp": n_dense, "mixer": dict(
+            lat, heads=H, rot={"base": 1e6, "dims": lat["rot_dim"]}, scale=(lat["dim"] + lat["rot_dim"]) ** -0.5,
+            mask={"size": window})}
+
+        def nuvivik(kinds):
+            return {"architecture": "Nuvivik", "vocab": vocab, "width": W, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+                    "logit_scale": 1.0, "logit_softcap": 30.0, "layers": kinds}
+
+        models.update({
+            "nuvivik-attention": nuvivik([n_attention] * layers),
+            "nuvivik-latent": nuvivik([n_latent] * layers),
+            "nuvivik-routed": nuvivik([dict(n_attention, mlp=n_routed)] * layers),
+            "nuvivik-mixed": nuvivik([n_latent, dict(n_latent, mlp=n_routed), n_latent, dict(n_attention, mlp=n_routed)]),
+        })
         if args.design_models:
             wanted = [w for w in args.design_models.split(",") if w]
             models = {name: raw for name, raw in models.items() if any(name.startswith(w) for w in wanted)}
@@ -651,11 +678,15 @@ def design_compare(args) -> int:
         mixer_cost["tekilorn-routed"] = mixer_cost["tekilorn-window"]
         mixer_cost["zabutar-recurrence"] = mixer_cost["zabutar-routed"] = mixer_cost["zofadra-recurrence"]
         mixer_cost["zabutar-attention"] = mixer_cost["qwen3"]
+        mixer_cost["nuvivik-attention"] = mixer_cost["nuvivik-routed"] = mixer_cost["qwen3-window"]
+        mixer_cost["nuvivik-latent"] = (2 * H * (2 * rank + rot) * seen(window), batch * window * (rank + rot) * 2)
         mixer_part = {"qwen3": "mixer.attention", "qwen3-window": "mixer.attention", "zofadra-attention": "mixer.attention",
                       "zofadra-latent": "mixer.attention", "zofadra-recurrence": "mixer.recurrence",
                       "tekilorn-differential": "mixer.attention", "tekilorn-window": "mixer.attention",
                       "tekilorn-routed": "mixer.attention", "zabutar-recurrence": "mixer.recurrence",
-                      "zabutar-routed": "mixer.recurrence", "zabutar-attention": "mixer.attention"}
+                      "zabutar-routed": "mixer.recurrence", "zabutar-attention": "mixer.attention",
+                      "nuvivik-attention": "mixer.attention", "nuvivik-routed": "mixer.attention",
+                      "nuvivik-latent": "mixer.attention"}
         for name, raw in models.items():
             n_layers = len(raw["layers"]) if "layers" in raw else raw["num_hidden_layers"]
             pages = batch * (-(-(CONTEXT + 64) // PAGE) + 1) + -(-CONTEXT // PAGE) + 8

@@ -77,6 +77,9 @@ struct AttnParams {
   // the score before it is scaled, so the table holds the bias divided by the scale.
   const float* dist_bias = nullptr;
   int dist_len = 0;
+  // above zero: the scaled score s becomes cap tanh(s / cap); the kernel works on unscaled
+  // products, so it is given cap / scale and scale / cap
+  float cap_over_scale = 0.f, scale_over_cap = 0.f;
 };
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) {
@@ -1176,7 +1179,8 @@ static __device__ __align__(256) float fe_noalloc_scratch[FE_NOALLOC_SCRATCH_FLO
 // entries with more than `row_lo` rows (new tokens x heads per kv head).  Beyond what
 // fe_attention_mma_d gives it: with a window, keys below `keep_first` stay visible; row
 // (token, head) of `out` is multiplied by sigmoid(gate[token * gate_stride + head]) (gate
-// null: no gate).  q rows are `q_stride` apart, out is [tokens, heads * D].  Returns
+// null: no gate); `softcap` above zero caps the scaled scores by softcap tanh(. / softcap) (not
+// together with dist_bias).  q rows are `q_stride` apart, out is [tokens, heads * D].  Returns
 // FE_ERR_BAD_SHAPE where the kernel's shapes do not hold (head size 64 or 128, heads per kv
 // head dividing 128, pages of 4 to 128 keys that divide 128).
 FE_EXPORT int SYM(fe_attention_prefill_tc5_d)(const void* q, int q_stride, void* out, const void* k_cache,
@@ -1184,10 +1188,11 @@ FE_EXPORT int SYM(fe_attention_prefill_tc5_d)(const void* q, int q_stride, void*
                                               int num_pages, int num_kv_heads, int groups, const int* cu_tokens,
                                               const int* starts, int entries, int max_new, int total_tokens, int window,
                                               int keep_first, float scale, const float* gate, long long gate_stride,
-                                              int row_lo, const float* dist_bias, int dist_len, int* status,
-                                              cudaStream_t stream) {
+                                              int row_lo, const float* dist_bias, int dist_len, float softcap,
+                                              int* status, cudaStream_t stream) {
   if (entries <= 0 || max_new * groups <= row_lo) return 0;
   if (dist_bias != nullptr && dist_len < 1) return FE_ERR_BAD_SHAPE;
+  if (softcap < 0.f || (softcap > 0.f && dist_bias != nullptr)) return FE_ERR_BAD_SHAPE;
   if (entries > 65535 || num_kv_heads > 65535) return FE_ERR_TOO_LARGE;
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return FE_ERR_BAD_ALIGN;
   if ((q_stride % 8) != 0) return FE_ERR_BAD_ALIGN;
@@ -1204,6 +1209,7 @@ FE_EXPORT int SYM(fe_attention_prefill_tc5_d)(const void* q, int q_stride, void*
   p.num_splits = 1; p.ws_acc = nullptr; p.ws_ml = nullptr; p.ws_count = nullptr; p.cluster_merge = 0;
   p.keep_first = keep_first; p.gate = gate; p.gate_stride = gate_stride;
   p.dist_bias = dist_bias; p.dist_len = dist_len;
+  if (softcap > 0.f) { p.cap_over_scale = softcap / scale; p.scale_over_cap = scale / softcap; }
   CUtensorMap mk, mv, mq;
   if (!cache_map(&mk, k_cache, num_pages * num_kv_heads * page_size, page_size) ||
       !cache_map(&mv, v_cache, num_pages * num_kv_heads * page_size, page_size) ||
@@ -1214,6 +1220,8 @@ FE_EXPORT int SYM(fe_attention_prefill_tc5_d)(const void* q, int q_stride, void*
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC5_SMEM);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC5_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC5_SMEM);
     if (e != cudaSuccess) return (int)e;
     tc5_configured = true;
   }
@@ -1222,7 +1230,9 @@ FE_EXPORT int SYM(fe_attention_prefill_tc5_d)(const void* q, int q_stride, void*
   const dim3 grid(num_kv_heads, entries, query_blocks);
   const int rc = dist_bias != nullptr
                      ? fe_launch_dependent(attn_prefill_tc5_kernel<true>, grid, dim3(TC5_THREADS), TC5_SMEM, stream, mq, mk, mv, p)
-                     : fe_launch_dependent(attn_prefill_tc5_kernel<false>, grid, dim3(TC5_THREADS), TC5_SMEM, stream, mq, mk, mv, p);
+                     : softcap > 0.f
+                           ? fe_launch_dependent(attn_prefill_tc5_kernel<false, true>, grid, dim3(TC5_THREADS), TC5_SMEM, stream, mq, mk, mv, p)
+                           : fe_launch_dependent(attn_prefill_tc5_kernel<false>, grid, dim3(TC5_THREADS), TC5_SMEM, stream, mq, mk, mv, p);
   return rc ? rc : fe_last_error();
 }
 

@@ -204,7 +204,18 @@ __device__ __forceinline__ Tc5Tile tc5_tile(int row0, int rows_total, int start,
   return t;
 }
 
-template <bool DIST_BIAS>     // with a learned bias by distance (AttnParams::dist_bias)
+// c tanh(x / c) through the hardware's approximate tanh (relative error about 2^-11): a capped score
+// is off by at most c 2^-11, below what rounding the weights to bfloat16 for the value product costs
+__device__ __forceinline__ float tc5_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// DIST_BIAS: with a learned bias by distance (AttnParams::dist_bias); SOFTCAP: scores capped by
+// cap tanh(score / cap) (AttnParams::cap_over_scale).  Each an instantiation of its own, so that
+// the plain one keeps its registers.
+template <bool DIST_BIAS, bool SOFTCAP = false>
 __global__ void __launch_bounds__(TC5_THREADS, 1)
 attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, AttnParams p) {
@@ -433,6 +444,13 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
         for (int j = 0; j < TC5_KEYS; ++j)
           raw[j] = __float_as_uint(__uint_as_float(raw[j]) + __ldg(bias_row + min(max(d0 - j, 0), far)));
+      }
+      if (SOFTCAP) {
+        // the raw product becomes (cap / scale) tanh(product scale / cap): everything below
+        // multiplies by the scale as before
+#pragma unroll
+        for (int j = 0; j < TC5_KEYS; ++j)
+          raw[j] = __float_as_uint(p.cap_over_scale * tc5_tanh(__uint_as_float(raw[j]) * p.scale_over_cap));
       }
       // every key of the tile visible to every row of the tile?
       const bool clear = key0 + TC5_KEYS - 1 <= mine.pos_first && key0 + TC5_KEYS <= mine.key_end &&

@@ -143,13 +143,14 @@ def attention_prefill_tc5(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
                           block_table: torch.Tensor, cu_tokens: torch.Tensor, starts: torch.Tensor, n_entries: int,
                           max_new: int, num_q_heads: int, window: int | None, keep_first: int, scale: float,
                           gate: torch.Tensor | None, row_lo: int, status: torch.Tensor,
-                          distance_bias: torch.Tensor | None = None) -> None:
+                          distance_bias: torch.Tensor | None = None, softcap: float | None = None) -> None:
     """The tcgen05 prefill attention for the entries of a step with more than ``row_lo`` rows
     (new tokens x heads per kv head): ``q`` [N, heads * D] and ``out`` [N, heads * D] bfloat16,
     caches [pages, kv_heads, page_size, D].  ``window`` with ``keep_first``: keys below it
     stay visible; ``gate`` (32-bit [N, >= heads]): sigmoid gates per (token, head);
     ``distance_bias`` (32-bit [heads, L]): entry min(query position - key position, L - 1) of the
-    head's row is added to the score before the scale, so it holds the bias over the scale."""
+    head's row is added to the score before the scale, so it holds the bias over the scale;
+    ``softcap`` c (not together with the bias): scaled scores become c tanh(score / c)."""
     _dense(q, "q"), _dense(out, "out"), _dense(k_cache, "k_cache"), _dense(v_cache, "v_cache"), _dense(block_table, "block_table")
     num_pages, nkv, page_size, d = k_cache.shape
     n = q.shape[0]
@@ -160,17 +161,18 @@ def attention_prefill_tc5(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
     fn = getattr(handle, f"fe_attention_prefill_tc5_d{d}")
     if not getattr(fn, "_declared", False):
         p, i, f, ll = c_void_p, c_int, c_float, ctypes.c_longlong
-        fn.argtypes = [p, i, p, p, p, p, i, i, i, i, i, p, p, i, i, i, i, i, f, p, ll, i, p, i, p, p]
+        fn.argtypes = [p, i, p, p, p, p, i, i, i, i, i, p, p, i, i, i, i, i, f, p, ll, i, p, i, f, p, p]
         fn.restype = c_int
         fn._declared = True
+    assert not (softcap and distance_bias is not None)
     assert distance_bias is None or (distance_bias.dtype == torch.float32 and distance_bias.is_contiguous()
                                      and distance_bias.dim() == 2 and distance_bias.shape[0] == num_q_heads)
     gate_stride = 0 if gate is None else (int(gate.stride(0)) if n > 1 else int(gate.shape[1]))
     check(fn(ptr(q), int(q.shape[1]), ptr(out), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.shape[1],
              page_size, num_pages, nkv, num_q_heads // nkv, ptr(cu_tokens), ptr(starts), int(n_entries), int(max_new), n,
              int(window or 0), int(keep_first or 0), float(scale), ptr(gate), gate_stride, int(row_lo),
-             ptr(distance_bias), 0 if distance_bias is None else int(distance_bias.shape[1]), ptr(status),
-             stream()), "attention_prefill_tc5")
+             ptr(distance_bias), 0 if distance_bias is None else int(distance_bias.shape[1]), float(softcap or 0.0),
+             ptr(status), stream()), "attention_prefill_tc5")
 
 
 def _attention_handle(head_dim: int):

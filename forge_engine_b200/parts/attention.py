@@ -376,7 +376,8 @@ class GQAttention(Mixer):
                 # prompt portions of a plain softmax layer with heads of 64 or 128: the tcgen05 kernel
                 native.attention_prefill_tc5(q, k_cache, v_cache, out, table, batch.cu_tokens, batch.starts, batch.n_entries,
                                              batch.max_new, nq, self.spec.window, self.keep_first, self.spec.scale, gate,
-                                             SHORT_ENTRY_ROWS, self.ctx.status, distance_bias=self.distance_bias_unscaled)
+                                             SHORT_ENTRY_ROWS, self.ctx.status, distance_bias=self.distance_bias_unscaled,
+                                             softcap=self.softcap)
             if short_entries:
                 native.attention_general(q, (nq * d, d), k_cache, self.d, v_cache, dv, out, (nq * parts * dv, parts * dv), table,
                                          batch.positions, batch.token_entry, nq, self.slopes, self.spec.window,
@@ -445,9 +446,10 @@ class GQAttention(Mixer):
 
     def _prefill_tc5(self, page_size: int) -> bool:
         """Whether prompt portions of this (general) layer run on the tcgen05 prefill kernel:
-        a plain softmax over one map per head (a window, kept first tokens, a gate per head and a
-        bias by distance it has), keys and values of 64 or 128."""
-        return (self.parts == 1 and self.slopes is None and self.softcap is None and self.query_temperature is None
+        a plain softmax over one map per head (a window, kept first tokens, a gate per head and
+        either a bias by distance or capped scores it has), keys and values of 64 or 128."""
+        return (self.parts == 1 and self.slopes is None and (self.softcap is None or self.distance_bias is None)
+                and self.query_temperature is None
                 and self.spec.scale > 0 and native.prefill_tc5_takes(self.ctx.dtype, self.d, self.dv, self.nq // self.nkv, page_size)
                 and native.general_mma_takes(self.ctx.dtype, self.d, self.dv))
 

@@ -124,6 +124,7 @@ SINGLE = {
     "attention_stretched": [pn.attention_layer(scaling=(8.0, 1.0, 4.0, 16), base=50.0)],
     "attention_odd_sizes": [pn.attention_layer(heads=3, kv_heads=1, dim=12, vdim=20, rot_dims=6)],
     "attention_heads_of_64": [pn.attention_layer(heads=2, kv_heads=2, dim=64, vdim=64, rot_dims=32)],
+    "attention_heads_of_128": [pn.attention_layer(heads=4, kv_heads=1, dim=128, vdim=128, rot_dims=64, softcap=8.0)],
     "attention_wide_values": [pn.attention_layer(heads=2, kv_heads=1, dim=16, vdim=48)],
     "attention_window_of_one": [pn.attention_layer(window=1)],
     "latent_dense": [pn.latent_layer()],
@@ -415,6 +416,8 @@ EDGE_LAYERS = {
     "attention": lambda window: pn.attention_layer(heads=4, kv_heads=2, dim=32, vdim=32, rot_dims=4, window=window, softcap=60.0, mlp=None),
     "attention_heads_of_64": lambda window: pn.attention_layer(heads=2, kv_heads=1, dim=64, vdim=64, rot_dims=8, window=window,
                                                                softcap=None, mlp=None),
+    "attention_heads_of_128_capped": lambda window: pn.attention_layer(heads=4, kv_heads=2, dim=128, vdim=128, rot_dims=16, window=window,
+                                                                       softcap=40.0, mlp=None),
     "latent": lambda window: pn.latent_layer(heads=2, dim=16, rot_dim=4, vdim=16, q_rank=32, kv_rank=72, window=window, mlp=None),
     "latent_sixteens": lambda window: pn.latent_layer(heads=4, dim=16, rot_dim=16, vdim=32, q_rank=64, kv_rank=128, window=window, mlp=None),
 }
@@ -429,7 +432,7 @@ def test_a_loud_key_just_inside_and_just_outside_the_window(tmp_path, kind, wind
     more a token later (the first that does not); in a whole prompt, in two portions cut
     between them, and decoded token by token; with pages of 4 and 16 tokens, so that the edge
     falls on, before and after a page border."""
-    cfg = pn.config([EDGE_LAYERS[kind](window)], width=192, vocab=40)
+    cfg = pn.config([EDGE_LAYERS[kind](window)], width=320 if "128" in kind else 192, vocab=40)
     key_token, query_token = 38, 39
 
     def change(weights):
