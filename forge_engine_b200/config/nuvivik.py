@@ -10,7 +10,8 @@ A layer: x += norm1(mixer(x)), x += norm2(ff(x)), both RMS norms with a weight. 
 is multiplied by ``embedding.scale``; the logits are head(final norm(x)) * ``logit_scale``,
 then c tanh(. / c) with c = ``logit_softcap``.
 
-Mixers (both causal with a sliding window of ``mask.size`` tokens, the query's own included):
+Mixers (both causal with a sliding window of ``mask.size`` tokens, the query's own included;
+without ``mask`` every earlier token is visible):
 
 * ``attention`` - grouped-query attention: q, k, v with biases; the first ``rot.dims``
   elements of every head rotated (element i with i + dims / 2, base ``rot.base``, frequencies
@@ -116,8 +117,11 @@ class NuvivikConfig:
             for key in ("heads", "dim", "vdim"):
                 _int(mixer, key, f"{where}.mixer")
             _number(mixer, "scale", f"{where}.mixer")
-            _int(mixer.get("mask") or {}, "size", f"{where}.mixer.mask")
+            if mixer.get("mask") is not None:                    # no mask: every earlier token is visible
+                _int(mixer["mask"], "size", f"{where}.mixer.mask")
             if kind == "attention":
+                if mixer.get("kv_heads") is None:
+                    mixer = dict(mixer, kv_heads=mixer["heads"])    # every query head with keys and values of its own
                 _int(mixer, "kv_heads", f"{where}.mixer")
                 if mixer["heads"] % mixer["kv_heads"]:
                     raise ConfigError(f"{where}.mixer.heads must be a multiple of kv_heads")
@@ -175,7 +179,7 @@ class NuvivikConfig:
 
     def _mixer_spec(self, layer: NuvivikLayer):
         m = layer.mixer
-        window = int(m["mask"]["size"])
+        window = None if m.get("mask") is None else int(m["mask"]["size"])
         if layer.type == "attention":
             return AttentionSpec(
                 hidden_size=self.width, num_heads=m["heads"], num_kv_heads=m["kv_heads"], head_dim=m["dim"], qk_norm=True,

@@ -81,6 +81,11 @@ def windowed_softmax(scores: torch.Tensor, window: int, sink=None) -> torch.Tens
 
 
 # -- mixers ------------------------------------------------------------------------------------
+def window_of(m: dict, length: int) -> int:
+    """The mixer's window; without a mask every earlier token is visible."""
+    return m["mask"]["size"] if m.get("mask") is not None else length
+
+
 def attention(h, w, prefix, m, eps):
     """Grouped-query attention: biased q/k/v, partial rotation, q and k divided by their root
     mean square after the rotation, capped scores, sliding window, plain softmax."""
@@ -98,7 +103,7 @@ def attention(h, w, prefix, m, eps):
         scores = (q[:, head] @ k[:, g].T) * m["scale"]
         if cap is not None:
             scores = cap * torch.tanh(scores / cap)
-        out[:, head] = windowed_softmax(scores, m["mask"]["size"]) @ v[:, g]
+        out[:, head] = windowed_softmax(scores, window_of(m, length)) @ v[:, g]
     return out.reshape(length, heads * vdim) @ w[prefix + "o"].T
 
 
@@ -119,7 +124,7 @@ def latent_attention(h, w, prefix, m, eps):
     out = torch.empty(length, heads, vdim, dtype=h.dtype)
     for head in range(heads):
         scores = (q_plain[:, head] @ k_plain[:, head].T + q_rot[:, head] @ k_rot.T) * m["scale"]
-        out[:, head] = windowed_softmax(scores, m["mask"]["size"], sink=w[prefix + "sink"][head]) @ v[:, head]
+        out[:, head] = windowed_softmax(scores, window_of(m, length), sink=w[prefix + "sink"][head]) @ v[:, head]
     return out.reshape(length, heads * vdim) @ w[prefix + "o"].T
 
 
@@ -259,6 +264,7 @@ def routed(experts=6, top=2, ff=24, groups=(3, 2)):
 
 def attention_layer(heads=4, kv_heads=2, dim=16, vdim=16, window=24, rot_dims=8, base=10000.0, scaling=None, scale=None,
                     softcap=15.0, mlp="dense"):
+    """``window`` None leaves the mask out: every earlier token is visible."""
     rot = {"base": base, "dims": rot_dims}
     if scaling is not None:
         rot["scaling"] = dict(zip(("factor", "low", "high", "original"), scaling))
@@ -266,6 +272,8 @@ def attention_layer(heads=4, kv_heads=2, dim=16, vdim=16, window=24, rot_dims=8,
              "scale": scale if scale is not None else 1.0 / math.sqrt(dim)}
     if softcap is not None:
         mixer["softcap"] = softcap
+    if window is None:
+        del mixer["mask"]
     return {"type": "attention", "mixer": mixer, "mlp": dense() if mlp == "dense" else mlp}
 
 
@@ -273,6 +281,8 @@ def latent_layer(heads=3, dim=16, rot_dim=8, vdim=24, q_rank=32, kv_rank=40, win
     mixer = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
              "mask": {"size": window}, "rot": {"base": base, "dims": rot_dim},
              "scale": scale if scale is not None else 1.0 / math.sqrt(dim + rot_dim)}
+    if window is None:
+        del mixer["mask"]
     return {"type": "latent_attention", "mixer": mixer, "mlp": dense() if mlp == "dense" else mlp}
 
 

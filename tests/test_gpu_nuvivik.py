@@ -324,6 +324,8 @@ OTHER = {
     "wide_latent": dict(layers=[pn.latent_layer(heads=2, dim=24, rot_dim=8, vdim=40, q_rank=96, kv_rank=136)], width=96),
     "scale_one_eps_large": dict(layers=[pn.attention_layer(scale=1.0), pn.latent_layer(scale=1.0)], eps=0.5),
     "windows_longer_than_the_sequence": dict(layers=[pn.attention_layer(window=500), pn.latent_layer(window=64)]),
+    "no_mask": dict(layers=[pn.attention_layer(window=None), pn.latent_layer(window=None), pn.attention_layer(heads=2, kv_heads=2, dim=64, vdim=64,
+                                                                                                            rot_dims=16, window=None)]),
     "top_equals_experts": dict(layers=[pn.latent_layer(mlp=pn.routed(experts=4, top=4, groups=(2, 2)))]),
     "many_experts": dict(layers=[pn.attention_layer(mlp=pn.routed(experts=40, top=5, ff=8, groups=(8, 3)))]),
     "latent_layers_only": dict(layers=[pn.latent_layer(window=9), pn.latent_layer(window=9, mlp=pn.routed(top=1)), pn.latent_layer(window=9)]),
