@@ -651,7 +651,7 @@ def design_compare(args) -> int:
 
         def nuvivik(kinds):
             return {"architecture": "Nuvivik", "vocab": vocab, "width": W, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
-                    "logit_scale": 1.0, "logit_softcap": 30.0, "layers": kinds}
+                    "logit_scale": 1.0, "logit_softcap": 50.0, "layers": kinds}
 
         models.update({
             "nuvivik-attention": nuvivik([n_attention] * layers),

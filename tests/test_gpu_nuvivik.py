@@ -421,7 +421,7 @@ EDGE_LAYERS = {
     "attention_heads_of_128_capped": lambda window: pn.attention_layer(heads=4, kv_heads=2, dim=128, vdim=128, rot_dims=16, window=window,
                                                                        softcap=40.0, mlp=None),
     "latent": lambda window: pn.latent_layer(heads=2, dim=16, rot_dim=4, vdim=16, q_rank=32, kv_rank=72, window=window, mlp=None),
-    "latent_sixteens": lambda window: pn.latent_layer(heads=4, dim=16, rot_dim=16, vdim=32, q_rank=64, kv_rank=128, window=window, mlp=None),
+    "latent_sixteens": lambda window: pn.latent_layer(heads=4, dim=16, rot_dim=16, vdim=32, q_rank=64, kv_rank=112, window=window, mlp=None),
 }
 
 
@@ -434,7 +434,7 @@ def test_a_loud_key_just_inside_and_just_outside_the_window(tmp_path, kind, wind
     more a token later (the first that does not); in a whole prompt, in two portions cut
     between them, and decoded token by token; with pages of 4 and 16 tokens, so that the edge
     falls on, before and after a page border."""
-    cfg = pn.config([EDGE_LAYERS[kind](window)], width=320 if "128" in kind else 192, vocab=40)
+    cfg = pn.config([EDGE_LAYERS[kind](window)], width=384 if "128" in kind else 192, vocab=40)
     key_token, query_token = 38, 39
 
     def change(weights):
